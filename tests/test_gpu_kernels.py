@@ -1,0 +1,194 @@
+"""Each CUDA kernel alone against its plain statement (tests/kernel_refs.py), at sizes
+other than the engine's: widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd head counts and groups, pages of several sizes."""
+import math
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from wllm_b200.kernels import ops as o
+    return o
+
+
+def tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,H,V", [(1, 64, 100), (37, 2050, 999), (5, 96, 7)])
+def test_embed_gather(dtype, n, H, V):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (n,), generator=g, dtype=torch.int32)
+    want = ref.embed_gather(ids, table, 3.25, torch.empty(n, H))
+    got = ops().embed_gather(ids.to(DEV), table.to(DEV), 3.25, torch.empty(n, H, device=DEV))
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,H", [(3, 64), (17, 2050), (2, 96), (4, 5000)])
+@pytest.mark.parametrize("offset,eps", [(1.0, 1e-6), (0.0, 1e-5)])
+def test_rmsnorm_with_and_without_delta_and_rows(dtype, n, H, offset, eps):
+    g = torch.Generator().manual_seed(1)
+    resid = torch.randn(n, H, generator=g) * 3
+    delta = torch.randn(n, H, generator=g).to(dtype)
+    w = (torch.randn(H, generator=g) * 0.1).to(dtype)
+    # with a delta: the residual is updated in place
+    r_ref, out_ref = resid.clone(), torch.empty(n, H, dtype=dtype)
+    ref.rmsnorm(r_ref, delta, w, eps, offset, out_ref)
+    r_dev, out_dev = resid.to(DEV), torch.empty(n, H, dtype=dtype, device=DEV)
+    ops().rmsnorm(r_dev, delta.to(DEV), w.to(DEV), eps, offset, out_dev)
+    assert torch.equal(r_dev.cpu(), r_ref)
+    torch.testing.assert_close(out_dev.cpu().float(), out_ref.float(), **tol(dtype))
+    # without: untouched
+    r_dev2, out2 = resid.to(DEV), torch.empty(n, H, dtype=dtype, device=DEV)
+    ops().rmsnorm(r_dev2, None, w.to(DEV), eps, offset, out2)
+    assert torch.equal(r_dev2.cpu(), resid)
+    torch.testing.assert_close(out2.cpu().float(), ref.rmsnorm(resid.clone(), None, w, eps, offset,
+                                                              torch.empty(n, H, dtype=dtype)).float(), **tol(dtype))
+    # selected rows, delta folded in but not written back
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32)
+    out3 = torch.empty(2, H, dtype=dtype, device=DEV)
+    r_dev3 = resid.to(DEV)
+    ops().rmsnorm(r_dev3, delta.to(DEV), w.to(DEV), eps, offset, out3, rows=rows.to(DEV))
+    assert torch.equal(r_dev3.cpu(), resid)
+    want3 = ref.rmsnorm(resid.clone(), delta, w, eps, offset, torch.empty(2, H, dtype=dtype), rows=rows)
+    torch.testing.assert_close(out3.cpu().float(), want3.float(), **tol(dtype))
+
+
+def test_rmsnorm_32bit_weight_under_bfloat16_output():
+    g = torch.Generator().manual_seed(2)
+    resid, w = torch.randn(5, 200, generator=g), torch.randn(200, generator=g) * 0.1
+    out = torch.empty(5, 200, dtype=torch.bfloat16, device=DEV)
+    ops().rmsnorm(resid.to(DEV), None, w.to(DEV), 1e-6, 1.0, out)
+    want = ref.rmsnorm(resid.clone(), None, w, 1e-6, 1.0, torch.empty(5, 200, dtype=torch.bfloat16))
+    torch.testing.assert_close(out.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(4, 1, 32, 32, 16), (3, 3, 48, 48, 32), (6, 2, 80, 40, 16), (8, 1, 256, 256, 64)])
+def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
+    g = torch.Generator().manual_seed(3)
+    n, pages = 21, 9
+    qkv = torch.randn(n, (nq + 2 * nkv) * hd, generator=g).to(dtype)
+    positions = torch.randint(0, 5000, (n,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * ps, generator=g)[:n].to(torch.int32)
+    slots[4] = -1   # this token writes nothing
+    theta = 500.0
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    k_ref = torch.zeros(pages, nkv, ps, hd, dtype=dtype)
+    v_ref = torch.zeros_like(k_ref)
+    qkv_ref = qkv.clone()
+    ref.rope_kv_write(qkv_ref, positions, slots, inv_freq, k_ref, v_ref, nq, nkv, hd, rot, ps)
+    qkv_dev, k_dev, v_dev = qkv.to(DEV), torch.zeros_like(k_ref, device=DEV), torch.zeros_like(v_ref, device=DEV)
+    ops().rope_kv_write(qkv_dev, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k_dev, v_dev, nq, nkv, hd, rot, ps)
+    t = dict(rtol=1e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+    torch.testing.assert_close(qkv_dev.cpu().float(), qkv_ref.float(), **t)
+    torch.testing.assert_close(k_dev.cpu().float(), k_ref.float(), **t)
+    assert torch.equal(v_dev.cpu(), v_ref)
+    # a layer that reads another layer's cache rotates q and writes no page
+    k2 = torch.zeros_like(k_dev)
+    ops().rope_kv_write(qkv.to(DEV), positions.to(DEV), None, inv_freq.to(DEV), k2, k2, nq, nkv, hd, rot, ps)
+    assert float(k2.abs().sum()) == 0.0
+
+
+def _paged_case(dtype, nq, nkv, hd, ps, ctx_lens, q_lens, seed, spike=False):
+    """Requests with `ctx` tokens in scattered pages; the last `q` of each are this step's queries."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(ctx_lens)
+    pages_each = [-(-c // ps) for c in ctx_lens]
+    num_pages = sum(pages_each) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    P = max(pages_each) + 1
+    table = torch.full((R, P), -1, dtype=torch.int32)
+    k_pages = torch.randn(num_pages, nkv, ps, hd, generator=g).to(dtype)
+    v_pages = torch.randn(num_pages, nkv, ps, hd, generator=g).to(dtype)
+    it = iter(perm)
+    for r in range(R):
+        for i in range(pages_each[r]):
+            table[r, i] = next(it)
+    token_req, positions = [], []
+    for r, (c, q) in enumerate(zip(ctx_lens, q_lens)):
+        token_req += [r] * q
+        positions += list(range(c - q, c))
+    n = len(token_req)
+    q = (torch.randn(n, nq * hd, generator=g) * (1.0 if not spike else 0.3)).to(dtype)
+    if spike:
+        # one far key per request gets a score that stands out: a kernel that misses it,
+        # or reads it from the wrong page, is far off
+        for r, c in enumerate(ctx_lens):
+            far = 1 if c > 2 else 0
+            page, off = int(table[r, far // ps]), far % ps
+            rows = [i for i, t in enumerate(token_req) if t == r]
+            k_pages[page, :, off, :] = 0
+            k_pages[page, :, off, 0] = 40.0
+            for i in rows:
+                q[i].view(nq, hd)[:, 0] = 6.0
+    return (q, k_pages, v_pages, torch.tensor(token_req, dtype=torch.int32),
+            torch.tensor(positions, dtype=torch.int32), table)
+
+
+ATTN_CASES = [
+    # nq nkv hd  ps  ctx_lens            q_lens
+    (4, 1, 32, 16, [1, 5, 16, 17, 33, 100], [1, 1, 1, 1, 1, 1]),
+    (3, 3, 48, 32, [70, 2, 130], [70, 2, 7]),
+    (8, 1, 256, 16, [300, 64, 65], [1, 64, 3]),
+    (6, 2, 80, 64, [129, 31], [129, 1]),
+    (16, 16, 128, 16, [40], [40]),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ATTN_CASES)
+@pytest.mark.parametrize("window", [0, 24])
+def test_paged_attention_simt(dtype, case, window):
+    nq, nkv, hd, ps, ctx_lens, q_lens = case
+    q, kp, vp, treq, pos, table = _paged_case(dtype, nq, nkv, hd, ps, ctx_lens, q_lens, seed=7, spike=(window == 0))
+    scale = 1.0 / math.sqrt(hd)
+    want = ref.paged_attention(q, torch.empty(q.shape[0], nq * hd, dtype=torch.float64), kp, vp, treq, pos, table,
+                               nq, nkv, hd, ps, window, scale, dtype=torch.float64)
+    got = torch.empty(q.shape[0], nq * hd, dtype=dtype, device=DEV)
+    ops().paged_attention_simt(q.to(DEV), got, kp.to(DEV), vp.to(DEV), treq.to(DEV), pos.to(DEV), table.to(DEV),
+                               nq, nkv, hd, ps, window, scale)
+    t = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+    torch.testing.assert_close(got.cpu().double(), want, **t)
+
+
+def test_paged_attention_refuses_unsupported_head_size():
+    from wllm_b200.kernels import KernelError
+    q = torch.zeros(1, 40, device=DEV)
+    kp = torch.zeros(1, 1, 16, 40, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="size not supported"):
+        ops().paged_attention_simt(q, torch.empty_like(q), kp, kp, z, z, z.view(1, 1), 1, 1, 40, 16, 0, 1.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("n,I", [(1, 256), (19, 384), (3, 1001)])
+def test_gated_act(dtype, act, n, I):
+    g = torch.Generator().manual_seed(4)
+    gu = (torch.randn(n, 2 * I, generator=g) * 2).to(dtype)
+    want = ref.gated_act(gu, torch.empty(n, I, dtype=dtype), act)
+    got = ops().gated_act(gu.to(DEV), torch.empty(n, I, dtype=dtype, device=DEV), act)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 64), (33, 1000, 96), (130, 257, 144), (7, 129, 50), (300, 300, 1027)])
+def test_gemm_f32_is_true_32bit_and_row_invariant(M, N, K):
+    g = torch.Generator().manual_seed(5)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    want = (a.double() @ w.double().t())
+    got = ops().gemm_f32(a.to(DEV), w.to(DEV)).cpu()
+    # 32-bit accumulation error grows with sqrt(K); a reduced-precision mode would be ~1e-3 off
+    assert float((got.double() - want).abs().max()) < 2e-6 * math.sqrt(K) * 10
+    # a row of the result does not depend on the other rows of the batch
+    alone = ops().gemm_f32(a[M // 2: M // 2 + 1].to(DEV), w.to(DEV)).cpu()
+    assert torch.equal(alone[0], got[M // 2])

@@ -1,0 +1,103 @@
+"""The engine on the GPU against the plain implementation, for every way of cutting the
+same requests into steps: whole; most in one step and the last 32 tokens singly;
+portions of changing size down to two tokens; and mixed, up to four live requests with
+so few pages that they are used again.  In 32-bit and in bfloat16, on both tiny
+configurations, in process and once through bin/trace_run."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import traces
+from helpers import make_folder, max_diff, plain_rows, random_requests
+from tiny_configs import CONFIGS, PAGE_SIZES
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LENGTHS = {"A": (7, 19, 33, 70, 41, 12, 90, 55, 66, 100), "B": (1, 4, 50, 64, 120, 37, 81, 2, 130, 77)}
+# float32: kernels and plain implementation differ in summation order only.
+# bfloat16: operands of every product are rounded to 8 bits of mantissa; logits of the
+# tiny models are of order 0.1, and the error of a row stays below 2e-2.
+TOL = {torch.float32: 3e-5, torch.bfloat16: 2e-2}
+MODES = {"whole": traces.whole, "tail": traces.tail_singly, "portions": traces.portions,
+         "mixed": lambda r: traces.mixed(r, seed=3)}
+
+
+@pytest.fixture(scope="module")
+def setups(tmp_path_factory):
+    out = {}
+    for name in ("A", "B"):
+        folder = make_folder(tmp_path_factory.mktemp("m"), name)
+        reqs = random_requests(name, LENGTHS[name], seed=5)
+        out[name] = (folder, reqs, plain_rows(folder, name, reqs))
+    return out
+
+
+def gpu_runner(folder, dtype, page_size, pages):
+    from wllm_b200.config import EngineConfig
+    from wllm_b200.engine import build_model, build_runner
+    eng = EngineConfig(dtype=dtype, block_size=page_size, max_num_seqs=8)
+    return build_runner(build_model(folder, eng.dtype, eng.device), eng, num_pages=pages)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", list(MODES))
+def test_every_cut_matches_plain(setups, dtype, name, mode):
+    folder, reqs, ref = setups[name]
+    steps = MODES[mode](reqs)
+    ps = PAGE_SIZES[name]
+    pages = -(-traces.peak_tokens(steps) // ps)
+    runner = gpu_runner(folder, dtype, ps, pages)
+    rows = traces.run_in_process(runner, steps)
+    assert max_diff(rows, ref) < TOL[dtype]
+    assert runner.cache.free_pages() == [pages]
+    if mode == "mixed":
+        assert runner.cache.groups[0].pool.takes > pages, "the trace must use pages again"
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_32bit_logits_do_not_depend_on_the_cut_at_all(setups, name):
+    """In the 32-bit path every reduction has a fixed order per row, so the four traces
+    agree bit for bit; any difference is a fault of the cache or the batch."""
+    folder, reqs, _ = setups[name]
+    ps = PAGE_SIZES[name]
+    base = None
+    for mode, make in MODES.items():
+        steps = make(reqs)
+        runner = gpu_runner(folder, torch.float32, ps, -(-traces.peak_tokens(steps) // ps))
+        rows = traces.run_in_process(runner, steps)
+        if base is None:
+            base = rows
+            continue
+        bad = [k for k in base if not torch.equal(base[k], rows[k])]
+        assert not bad, f"{mode}: first differing (request, position): {sorted(bad)[0]}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(setups, tmp_path, dtype):
+    folder, reqs, ref = setups["B"]
+    steps = traces.mixed(reqs, seed=9)
+    out = tmp_path / "out"
+    lines = "".join(json.dumps(s) + "\n" for s in steps)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", str(traces.peak_tokens(steps))],
+                          input=lines, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    vocab = CONFIGS["B"]["vocab_size"]
+    pos, rows = {}, {}
+    for s in steps:
+        keys = []
+        for e in s["entries"]:
+            p0 = pos.get(e["id"], 0)
+            keys += [(e["id"], p0 + w) for w in e["want"]]
+            pos[e["id"]] = p0 + len(e["tokens"])
+        data = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(len(keys), vocab)
+        for k, row in zip(keys, data):
+            rows[k] = torch.from_numpy(row.copy())
+    assert max_diff(rows, ref) < TOL[torch.float32 if dtype == "float32" else torch.bfloat16]

@@ -1,0 +1,35 @@
+// Gated feed-forward activation on a fused [gate | up] row:
+//     out[n, c] = act(gate[n, c]) * up[n, c],   gate = in[n, c], up = in[n, I + c]
+// evaluated in 32-bit and rounded once.  act 0: tanh-approximated GELU
+//     0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)));  act 1: SiLU  x / (1 + exp(-x)).
+#include "common.cuh"
+
+__device__ __forceinline__ float act_gelu_tanh(float x) {
+    const float k = 0.7978845608028654f;  // sqrt(2/pi)
+    return 0.5f * x * (1.0f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float act_silu(float x) { return x / (1.0f + expf(-x)); }
+
+template <typename T, int ACT>
+__global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / I, c = idx % I;
+        const float g = to_f32(in[n * 2 * I + c]), u = to_f32(in[n * 2 * I + I + c]);
+        out[idx] = from_f32<T>((ACT == 0 ? act_gelu_tanh(g) : act_silu(g)) * u);
+    }
+}
+
+WLLM_API int wllm_gated_act(const void* in, void* out, int dtype, int act, int n, int I, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (I <= 0) return WLLM_BAD_SIZE;
+    if (act != 0 && act != 1) return WLLM_BAD_SIZE;
+    const size_t total = (size_t)n * I;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+#define LAUNCH(T, A) gated_act_kernel<T, A><<<blocks, threads, 0, stream>>>((const T*)in, (T*)out, I, total)
+    if (dtype == WLLM_BF16) { if (act == 0) LAUNCH(bf16, 0); else LAUNCH(bf16, 1); }
+    else if (dtype == WLLM_F32) { if (act == 0) LAUNCH(float, 0); else LAUNCH(float, 1); }
+    else return WLLM_BAD_DTYPE;
+#undef LAUNCH
+    return wllm_launch_status();
+}

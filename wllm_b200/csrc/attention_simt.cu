@@ -1,0 +1,149 @@
+// Attention over the paged cache, one warp per (token, query head), every size.
+//
+// A token at position p of request r attends to the keys first..p of r, where
+// first = 0, or p - window + 1 when the layer has a window; the keys are found
+// through the request's row of the block table.  The keys and values of this
+// step's own tokens are already in the pages when the kernel runs, so a portion
+// of a prompt, a whole prompt and a single decoded token are the same case.
+//
+// Scores, softmax statistics and the output accumulate in 32-bit (expf, no fast
+// math).  Keys are walked in tiles of 32 that start at absolute multiples of 32,
+// and every reduction has a fixed order, so a token's output depends on its own
+// query and keys only: not on what else is in the batch, nor on how the sequence
+// was cut into steps, nor on which pages hold it.
+//
+// Used for the 32-bit path at every size, and for bfloat16 at the sizes that the
+// tensor-core kernels refuse.
+#include "common.cuh"
+
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float* out) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+};
+template <> struct Vec<bf16> {
+    static constexpr int N = 8;
+    __device__ static void load(const bf16* p, float* out) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h[i]);
+            out[2 * i] = f.x; out[2 * i + 1] = f.y;
+        }
+    }
+};
+
+constexpr int WARPS = 4;
+
+template <typename T, int NE>  // head_dim <= 32 * NE
+__global__ void __launch_bounds__(WARPS * 32)
+paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                            const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                            const int* __restrict__ token_req, const int* __restrict__ positions,
+                            const int* __restrict__ block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
+                            int page_size, int window, float scale) {
+    extern __shared__ float q_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * WARPS + warp;
+    if (item >= n_tokens * nq) return;
+    const int token = item / nq, head = item % nq;
+    const int kvh = head / (nq / nkv);
+    const int pos = positions[token];
+    const int* table = block_table + (size_t)token_req[token] * max_pages;
+    float* qs = q_smem + warp * hd;
+    const T* qrow = q + (size_t)token * q_stride + (size_t)head * hd;
+    for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qrow[d]);
+    __syncwarp();
+
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    float m = -INFINITY, l = 0.f;
+    float o[NE];
+#pragma unroll
+    for (int e = 0; e < NE; ++e) o[e] = 0.f;
+
+    for (int tile = (first >> 5) << 5; tile <= pos; tile += 32) {
+        const int key = tile + lane;
+        const bool valid = key >= first && key <= pos;
+        float s = -INFINITY;
+        int row = -1;  // index of the key's row of head_dim elements inside the pool
+        if (valid) {
+            const int page = table[key / page_size];
+            row = (page * nkv + kvh) * page_size + key % page_size;
+            const T* kr = k_pages + (size_t)row * hd;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float kv[Vec<T>::N];
+            for (int d = 0; d < hd; d += Vec<T>::N) {
+                Vec<T>::load(kr + d, kv);
+#pragma unroll
+                for (int i = 0; i < Vec<T>::N; ++i) acc[i & 3] = fmaf(qs[d + i], kv[i], acc[i & 3]);
+            }
+            s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) * scale;
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int e = 0; e < NE; ++e) o[e] *= corr;
+        const int count = min(32, pos - tile + 1);
+        for (int j = 0; j < count; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            const int rj = __shfl_sync(0xffffffffu, row, j);
+            if (rj < 0) continue;
+            const T* vr = v_pages + (size_t)rj * hd;
+#pragma unroll
+            for (int e = 0; e < NE; ++e) {
+                const int d = e * 32 + lane;
+                if (d < hd) o[e] = fmaf(pj, to_f32(vr[d]), o[e]);
+            }
+        }
+        m = m_new;
+    }
+    T* orow = out + (size_t)token * out_stride + (size_t)head * hd;
+    const float inv_l = 1.0f / l;
+#pragma unroll
+    for (int e = 0; e < NE; ++e) {
+        const int d = e * 32 + lane;
+        if (d < hd) orow[d] = from_f32<T>(o[e] * inv_l);
+    }
+}
+
+template <typename T>
+static int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
+                  const int* token_req, const int* positions, const int* block_table, int max_pages, int n_tokens,
+                  int nq, int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
+    const int blocks = (n_tokens * nq + WARPS - 1) / WARPS;
+    const size_t smem = (size_t)WARPS * hd * sizeof(float);
+#define GO(NE) paged_attention_simt_kernel<T, NE><<<blocks, WARPS * 32, smem, stream>>>( \
+        (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, positions, \
+        block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale)
+    if (hd <= 64) GO(2);
+    else if (hd <= 128) GO(4);
+    else if (hd <= 256) GO(8);
+    else GO(16);
+#undef GO
+    return wllm_launch_status();
+}
+
+WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                       const void* v_pages, int dtype, const int* token_req, const int* positions,
+                                       const int* block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
+                                       int page_size, int window, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return WLLM_OK;
+    // rows are read with 16-byte loads: head sizes come in steps of 16 up to 512
+    if (hd <= 0 || hd > 512 || hd % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0)
+        return WLLM_BAD_SIZE;
+    if (dtype == WLLM_BF16) {
+        if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
+        return launch<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
+                            n_tokens, nq, nkv, hd, page_size, window, scale, stream);
+    }
+    if (dtype == WLLM_F32)
+        return launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
+                             n_tokens, nq, nkv, hd, page_size, window, scale, stream);
+    return WLLM_BAD_DTYPE;
+}

@@ -1,0 +1,65 @@
+// Shared by every kernel family: element types, status codes, reductions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define WLLM_API extern "C" __attribute__((visibility("default")))
+
+// Status codes returned by every entry point (0 = launched).  Values of 1000 and
+// above are 1000 + the cudaError_t of the failed launch.
+#define WLLM_OK 0
+#define WLLM_BAD_DTYPE 1
+#define WLLM_BAD_SIZE 2
+#define WLLM_BAD_ALIGN 3
+
+// Element types as the Python side names them.
+#define WLLM_F32 0
+#define WLLM_BF16 1
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+static inline int wllm_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? WLLM_OK : 1000 + (int)e;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block in a fixed order: xor tree inside each warp, then every thread
+// adds the warps' partial sums in warp order.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    return total;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    v = warp_max(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = -INFINITY;
+    for (int w = 0; w < nwarps; ++w) total = fmaxf(total, scratch[w]);
+    return total;
+}

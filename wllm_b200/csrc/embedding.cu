@@ -1,0 +1,31 @@
+// Scaled embedding gather: out[n, :] = float(table[ids[n], :]) * scale, written to the
+// 32-bit residual stream.  One block per token, 16-byte loads where the row allows.
+#include "common.cuh"
+
+template <typename T>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table, float scale,
+                                    float* __restrict__ out, int H, int V) {
+    const int row = blockIdx.x;
+    int id = ids[row];
+    float* o = out + (size_t)row * H;
+    if (id < 0 || id >= V) {  // the host checks ids; an id that slips through reads nothing
+        for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)id * H;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = to_f32(src[c]) * scale;
+}
+
+WLLM_API int wllm_embed_gather(const int* ids, const void* table, int table_dtype, float scale, float* out,
+                               int n, int H, int V, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    if (H <= 0 || V <= 0) return WLLM_BAD_SIZE;
+    const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+    if (table_dtype == WLLM_BF16)
+        embed_gather_kernel<bf16><<<n, threads, 0, stream>>>(ids, (const bf16*)table, scale, out, H, V);
+    else if (table_dtype == WLLM_F32)
+        embed_gather_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, scale, out, H, V);
+    else
+        return WLLM_BAD_DTYPE;
+    return wllm_launch_status();
+}

@@ -1,0 +1,186 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+`ModelRunner.step(entries)` takes portions of prompts beside single decoded tokens,
+cut anywhere, runs exactly the tokens it is given against the cache that earlier
+steps left, and returns the 32-bit logits at the wanted places (device tensor
+[wanted, vocab], in the order of the entries and of their `want`).  It reserves the
+pages for the whole batch first (all or nothing: `OutOfPages` leaves everything as
+it was), builds the batch's index arrays on the host, sends them in one copy, runs
+the model, and commits the new tokens.
+
+The reference has three separate forwards instead (whole prompt, one portion, batch
+of decoded tokens: src/wllm/models/llama.py:448-560) and never mixes them in one pass.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, RequestCache
+from ..kernels import ops
+from .model import ComposedModel
+
+
+@dataclass
+class StepEntry:
+    cache: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepContext:
+    """The batch as the parts see it: index arrays on the device, the cache, scratch buffers."""
+
+    def __init__(self, runner: "ModelRunner"):
+        self.runner = runner
+        self.cache = runner.cache
+        self.n_tokens = self.n_requests = 0
+        self.token_ids = self.positions = self.token_req = self.want_rows = None
+        self.req_q_start = self.req_q_len = self.req_ctx_len = self.req_slot = None
+        self.group_slots: list = []
+        self.group_tables: list = []
+        self.host = None   # the same arrays on the host, for launch decisions
+
+    def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        return self.runner.workspace(name, shape, dtype)
+
+    def state(self, name: str) -> torch.Tensor:
+        return self.cache.slots.tensors[name]
+
+    def attention(self, q, out, k_pages, v_pages, group: int, nq: int, nkv: int, hd: int, window: int, scale: float):
+        ops.paged_attention_simt(q, out, k_pages, v_pages, self.token_req, self.positions, self.group_tables[group],
+                                 nq, nkv, hd, self.cache.page_size, window, scale)
+
+
+class ModelRunner:
+    def __init__(self, model: ComposedModel, cache: CacheManager, device):
+        if not model.loaded:
+            raise RuntimeError("the model's weights are not loaded")
+        self.model, self.cache, self.device = model, cache, torch.device(device)
+        self._arena: dict = {}
+        self._pinned = None
+        self._meta = None
+        self.steps = 0
+        self.tokens_run = 0
+
+    def workspace(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= s
+        key = (name, dtype)
+        buf = self._arena.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._arena[key] = buf
+        return buf[:n].view(shape)
+
+    # -- batch building --------------------------------------------------------------
+    def _build(self, entries: list) -> StepContext:
+        cache, ps = self.cache, self.cache.page_size
+        G, R = len(cache.groups), len(entries)
+        lens = [len(e.tokens) for e in entries]
+        N = sum(lens)
+        M = sum(len(e.want) for e in entries)
+        P = max(1, max(len(t) for e in entries for t in e.cache.tables) if G else 1)
+
+        def pad(n):
+            return (n + 3) & ~3
+        sizes = [("token_ids", N), ("positions", N), ("token_req", N)] + [(f"slots{g}", N) for g in range(G)] + \
+                [("req_q_start", R), ("req_q_len", R), ("req_ctx_len", R), ("req_slot", R), ("want_rows", M)] + \
+                [(f"table{g}", R * P) for g in range(G)]
+        offsets, total = {}, 0
+        for name, n in sizes:
+            offsets[name] = (total, n)
+            total += pad(n)
+        host = np.zeros(total, dtype=np.int32)
+
+        def view(name):
+            o, n = offsets[name]
+            return host[o:o + n]
+        start = 0
+        wants = []
+        for r, e in enumerate(entries):
+            n, base = lens[r], e.cache.num_tokens
+            view("token_ids")[start:start + n] = e.tokens
+            view("positions")[start:start + n] = np.arange(base, base + n, dtype=np.int32)
+            view("token_req")[start:start + n] = r
+            for g in range(G):
+                table = np.asarray(e.cache.tables[g], dtype=np.int64)
+                pos = np.arange(base, base + n, dtype=np.int64)
+                view(f"slots{g}")[start:start + n] = table[pos // ps] * ps + pos % ps
+                view(f"table{g}").reshape(R, P)[r, :len(table)] = table
+            view("req_q_start")[r], view("req_q_len")[r] = start, n
+            view("req_ctx_len")[r], view("req_slot")[r] = base + n, e.cache.slot
+            wants.extend(start + w for w in e.want)
+            start += n
+        view("want_rows")[:] = wants
+
+        if self._pinned is None or self._pinned.numel() < total:
+            cap = max(total, 4096)
+            self._pinned = torch.empty(cap, dtype=torch.int32).pin_memory() if self.device.type == "cuda" \
+                else torch.empty(cap, dtype=torch.int32)
+            self._meta = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._pinned[:total].copy_(torch.from_numpy(host))
+        self._meta[:total].copy_(self._pinned[:total], non_blocking=True)
+        self.h2d_bytes = total * 4
+
+        ctx = StepContext(self)
+        ctx.n_tokens, ctx.n_requests, ctx.host = N, R, {k: view(k) for k, _ in sizes}
+        ctx.host["max_pages"] = P
+
+        def dev(name):
+            o, n = offsets[name]
+            return self._meta[o:o + n]
+        ctx.token_ids, ctx.positions, ctx.token_req = dev("token_ids"), dev("positions"), dev("token_req")
+        ctx.req_q_start, ctx.req_q_len = dev("req_q_start"), dev("req_q_len")
+        ctx.req_ctx_len, ctx.req_slot, ctx.want_rows = dev("req_ctx_len"), dev("req_slot"), dev("want_rows")
+        ctx.group_slots = [dev(f"slots{g}") for g in range(G)]
+        ctx.group_tables = [dev(f"table{g}").view(R, P) for g in range(G)]
+        return ctx
+
+    def _validate(self, entries: list) -> None:
+        vocab, limit = self.model.plan.vocab_size, self.model.plan.max_positions
+        seen = set()
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.cache.request_id!r}: an entry needs at least one token")
+            if id(e.cache) in seen:
+                raise ValueError(f"request {e.cache.request_id!r} appears twice in one step")
+            seen.add(id(e.cache))
+            if e.cache.closed:
+                raise ValueError(f"request {e.cache.request_id!r} is closed")
+            if e.cache.num_tokens + n > limit:
+                raise ValueError(f"request {e.cache.request_id!r}: {e.cache.num_tokens + n} tokens exceed the "
+                                 f"model's {limit} positions")
+            lo, hi = min(e.tokens), max(e.tokens)
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"request {e.cache.request_id!r}: token id {lo if lo < 0 else hi} outside the "
+                                 f"vocabulary of {vocab}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.cache.request_id!r}: wanted place {w} outside its {n} tokens")
+
+    # -- the step ----------------------------------------------------------------------
+    @torch.inference_mode()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        entries = list(entries)
+        if not entries:
+            return torch.empty((0, self.model.plan.vocab_size), dtype=torch.float32, device=self.device)
+        self._validate(entries)
+        self.cache.reserve([(e.cache, len(e.tokens)) for e in entries])   # all or nothing
+        try:
+            ctx = self._build(entries)
+            logits = self.model.forward(ctx)
+        except BaseException:
+            for e in entries:          # a failed step holds no pages beyond its committed tokens
+                self.cache.cancel_reservation(e.cache)
+            raise
+        for e in entries:
+            self.cache.commit(e.cache, len(e.tokens))
+        self.steps += 1
+        self.tokens_run += ctx.n_tokens
+        return logits

@@ -1,0 +1,177 @@
+"""Python faces of the CUDA kernels: one function per entry point.
+
+Each function checks what the kernel cannot (device, layout, element type), passes
+raw pointers and the current CUDA stream, and turns a non-zero status into an
+exception.  Nothing here computes: without a CUDA device or the compiled
+extension the functions raise; there is no other implementation to fall back to.
+The parts of a model call these through the module (`ops.rmsnorm(...)`), so a test
+can put a stand-in in a function's place.
+
+`launches` counts the kernel launches issued through this module (a captured CUDA
+graph replays its launches without passing here; the engine adds those itself).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .build import KernelBuildError, load_family
+
+launches = 0
+
+_F32, _BF16 = 0, 1
+_STATUS = {1: "element type not supported", 2: "size not supported", 3: "pointer or stride not aligned",
+           4: "size beyond the entry point's fixed scratch", 5: "device set-up failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"element type {t.dtype} not supported (float32 or bfloat16)")
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the engine's kernels run on a CUDA device only; got a tensor on " + str(t.device))
+
+
+def _ptr(t) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str) -> None:
+    global launches
+    if status == 0:
+        launches += 1
+        return
+    if status >= 1000:
+        raise KernelError(f"{what}: CUDA launch failed with error {status - 1000}")
+    raise KernelError(f"{what}: {_STATUS.get(status, 'status ' + str(status))}")
+
+
+def _int32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+    return t
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> torch.Tensor:
+    """out[n, :] = float(table[ids[n], :]) * scale; `out` is the float32 residual stream."""
+    _need_cuda(ids, table, out)
+    n, (V, H) = ids.shape[0], table.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (n, H) and table.is_contiguous()
+    lib = load_family("embedding")
+    _check(lib.wllm_embed_gather(_ptr(_int32(ids, "ids")), _ptr(table), _dt(table), c_float(scale), _ptr(out),
+                                 n, H, V, _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset: float, out: torch.Tensor,
+            rows=None) -> torch.Tensor:
+    """Fold `delta` into the residual (when given), then norm: see csrc/norm.cu."""
+    _need_cuda(resid, delta, weight, out, rows)
+    H = resid.shape[1]
+    n = rows.shape[0] if rows is not None else resid.shape[0]
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
+    assert weight.shape == (H,) and weight.is_contiguous()
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.is_contiguous()
+    lib = load_family("norm")
+    _check(lib.wllm_rmsnorm(_ptr(resid), _ptr(delta), _dt(delta) if delta is not None else _F32, _ptr(weight),
+                            _dt(weight), c_float(eps), c_float(offset), _ptr(out), _dt(out),
+                            _ptr(_int32(rows, "rows") if rows is not None else None), n, H, _stream()), "rmsnorm")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor, k_pages, v_pages,
+                  nq: int, nkv: int, hd: int, rot_dim: int, page_size: int) -> None:
+    """Rotate q and k inside the fused rows `qkv` [n, (nq+2nkv)*hd]; write k, v to the pages."""
+    _need_cuda(qkv, positions, slots, inv_freq, k_pages, v_pages)
+    n = qkv.shape[0]
+    assert qkv.stride(1) == 1 and qkv.shape[1] == (nq + 2 * nkv) * hd
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
+    if slots is not None:
+        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype == v_pages.dtype
+    lib = load_family("rope_cache")
+    _check(lib.wllm_rope_kv_write(_ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(_int32(positions, "positions")),
+                                  _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
+                                  _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size, _stream()),
+           "rope_kv_write")
+
+
+def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                         token_req: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+                         nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float) -> torch.Tensor:
+    """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd]."""
+    _need_cuda(q, out, k_pages, v_pages, token_req, positions, block_table)
+    n = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
+    lib = load_family("attention_simt")
+    _check(lib.wllm_paged_attention_simt(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                         _dt(q), _ptr(_int32(token_req, "token_req")),
+                                         _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
+                                         block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
+                                         _stream()), f"paged_attention_simt(head_dim={hd}, heads={nq}/{nkv})")
+    return out
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tensor:
+    """out[n, c] = act(gate_up[n, c]) * gate_up[n, I + c]."""
+    _need_cuda(gate_up, out)
+    n, two_i = gate_up.shape
+    assert gate_up.is_contiguous() and out.is_contiguous() and out.shape == (n, two_i // 2) and out.dtype == gate_up.dtype
+    code = {"gelu_tanh": 0, "silu": 1}.get(act)
+    if code is None:
+        raise KernelError(f"activation {act!r} not supported (gelu_tanh, silu)")
+    lib = load_family("activation")
+    _check(lib.wllm_gated_act(_ptr(gate_up), _ptr(out), _dt(gate_up), code, n, two_i // 2, _stream()), "gated_act")
+    return out
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T in true 32-bit arithmetic (csrc/gemm_f32.cu)."""
+    _need_cuda(a, w, out)
+    assert a.dtype == torch.float32 and w.dtype == torch.float32 and a.stride(1) == 1 and w.stride(1) == 1
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    assert out.stride(1) == 1 and out.shape == (M, N) and out.dtype == torch.float32
+    lib = load_family("gemm_f32")
+    _check(lib.wllm_gemm_f32(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()),
+           "gemm_f32")
+    return out
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a @ w^T in the element type of the operands.
+
+    float32: this engine's own FMA kernel (no reduced-precision matrix mode can
+    reach it).  bfloat16: the vendor's matrix library with 32-bit accumulation,
+    as the reference engine does for every projection (src/wllm/models/llama.py:95-98).
+    """
+    if a.dtype == torch.float32:
+        return gemm_f32(a, w, out)
+    _need_cuda(a, w)
+    global launches
+    launches += 1
+    return torch.matmul(a, w.t(), out=out) if out is not None else torch.matmul(a, w.t())
+
+
+__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
+           "gated_act", "gemm_f32", "linear"]
