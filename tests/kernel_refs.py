@@ -40,7 +40,7 @@ def rope_kv_write(qkv, positions, slots, inv_freq, k_pages, v_pages, nq, nkv, hd
     qk[..., :half] = x1 * cos - x2 * sin
     qk[..., half:rot_dim] = x2 * cos + x1 * sin
     rounded = x.to(qkv.dtype)
-    qkv[:, : (nq + nkv) * hd] = rounded[:, : nq + nkv].reshape(n, -1)
+    qkv[:, : nq * hd] = rounded[:, :nq].reshape(n, -1)   # rotated keys go to the pages only
     if slots is None:
         return
     for t in range(n):

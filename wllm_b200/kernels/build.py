@@ -51,9 +51,8 @@ def _build_dir() -> str:
     for cand in (first, os.path.join(tempfile.gettempdir(), f"wllm_b200_build_{os.getuid()}")):
         try:
             os.makedirs(cand, exist_ok=True)
-            probe = os.path.join(cand, f".w{os.getpid()}")
-            with open(probe, "w"):
-                pass
+            fd, probe = tempfile.mkstemp(prefix=".probe", dir=cand)
+            os.close(fd)
             os.unlink(probe)
             return cand
         except OSError:
@@ -69,7 +68,7 @@ def _key(source: str, flags: list[str]) -> str:
     h = hashlib.sha256()
     for path in [source] + _headers():
         with open(path, "rb") as f:
-            h.update(path.encode() + b"\0" + f.read() + b"\0")
+            h.update(os.path.basename(path).encode() + b"\0" + f.read() + b"\0")
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + flags).encode())
     return h.hexdigest()[:16]
 
@@ -92,8 +91,8 @@ def compile_family(family: str, defines: dict | None = None, verbose: bool = Tru
             return os.path.join(cand, name)
     out_dir = _build_dir()
     out = os.path.join(out_dir, name)
-    with open(os.path.join(out_dir, ".lock"), "w") as lockfile:
-        fcntl.flock(lockfile, fcntl.LOCK_EX)   # one compile at a time per folder; the others wait and then find the file
+    with open(out + ".lock", "w") as lockfile:
+        fcntl.flock(lockfile, fcntl.LOCK_EX)   # one compile per object; a second process waits and then finds the file
         try:
             if os.path.isfile(out):
                 return out

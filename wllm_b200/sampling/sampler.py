@@ -1,0 +1,77 @@
+"""Runs the sampling kernel over the logits rows of a step.
+
+One launch for all rows: per-row options, seeds, counters and the distinct generated
+ids (for the repetition penalty) travel in one int32 buffer; tokens and
+log-probabilities come back in one small copy.  The logits rows are modified in place
+where a repetition penalty applies.
+"""
+from __future__ import annotations
+
+from ctypes import c_void_p
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..kernels.build import load_family
+from .params import SamplingParams
+
+
+class Sampler:
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._pinned = self._dev = self._out = self._out_host = None
+        self.d2h_bytes = 0
+
+    def sample(self, logits: torch.Tensor, params: list, counters: list, seeds: list, generated: list):
+        """logits [rows, vocab] float32 on the device; params[i]: SamplingParams; counters[i]: index of
+        the output token being drawn; seeds[i]: the request's 64-bit seed; generated[i]: its distinct
+        generated ids (read only when its repetition penalty is not 1).  Returns (tokens, logprobs) lists."""
+        rows, V = logits.shape
+        if rows == 0:
+            return [], []
+        if logits.dtype != torch.float32 or logits.stride(1) != 1:
+            raise ops.KernelError("sampling needs float32 logits with unit stride along the vocabulary")
+        gen_lists = [sorted(g) if p.repetition_penalty != 1.0 else [] for p, g in zip(params, generated)]
+        offsets = np.zeros(rows + 1, dtype=np.int32)
+        offsets[1:] = np.cumsum([len(g) for g in gen_lists])
+        n_gen = int(offsets[-1])
+        total = 8 * rows + (rows + 1) + n_gen
+        host = np.zeros(total, dtype=np.int32)
+        f = host.view(np.float32)
+        f[0:rows] = [p.temperature for p in params]
+        host[rows:2 * rows] = [p.top_k for p in params]
+        f[2 * rows:3 * rows] = [p.top_p for p in params]
+        f[3 * rows:4 * rows] = [p.min_p for p in params]
+        f[4 * rows:5 * rows] = [p.repetition_penalty for p in params]
+        s = np.asarray([x & 0xFFFFFFFFFFFFFFFF for x in seeds], dtype=np.uint64)
+        host[5 * rows:6 * rows] = (s & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)
+        host[6 * rows:7 * rows] = (s >> np.uint64(32)).astype(np.uint32).view(np.int32)
+        host[7 * rows:8 * rows] = counters
+        host[8 * rows:9 * rows + 1] = offsets
+        if n_gen:
+            host[9 * rows + 1:] = np.concatenate([np.asarray(g, dtype=np.int32) for g in gen_lists if g])
+        if self._pinned is None or self._pinned.numel() < total:
+            cap = max(total, 8192)
+            self._pinned = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        if self._out is None or self._out.numel() < 2 * rows:
+            cap = max(2 * rows, 1024)
+            self._out = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._out_host = torch.empty(cap, dtype=torch.int32).pin_memory()
+        self._pinned[:total].copy_(torch.from_numpy(host))
+        self._dev[:total].copy_(self._pinned[:total], non_blocking=True)
+        base = self._dev.data_ptr()
+
+        def at(i):
+            return c_void_p(base + 4 * i)
+        lib = load_family("sampling")
+        ops._check(lib.wllm_sample(c_void_p(logits.data_ptr()), logits.stride(0), rows, V, at(0), at(rows), at(2 * rows),
+                                   at(3 * rows), at(4 * rows), at(5 * rows), at(6 * rows), at(7 * rows), at(8 * rows),
+                                   at(9 * rows + 1), c_void_p(self._out.data_ptr()),
+                                   c_void_p(self._out.data_ptr() + 4 * rows), ops._stream()), "sample")
+        self._out_host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes = 8 * rows
+        out = self._out_host[:2 * rows].numpy()
+        return out[:rows].tolist(), out[rows:].view(np.float32).tolist()
