@@ -1,0 +1,306 @@
+"""Gemma-2B decode and prefill throughput on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 8192] [--layers L]
+
+A step is one decode step of `batch` requests whose caches hold `context` tokens.
+Prints ONE JSON line: `value` = decoded tokens per second timed on the device with CUDA
+events over exactly K steps; `e2e` = the same through the Python entry point
+(`LLM.step`: pinned host index arrays in, sampled token ids out, every step);
+`prefill` = one prompt of 2,048 tokens; `roofline` = bytes a decode step has to read
+(every weight once and the live requests' cache) over its time, against the measured copy
+bandwidth; `points` = decode at batch 1 and 64.  Weights are random N(0, 0.02), token ids
+are seeded uniform random, the caches of the device-timed runs are filled with random
+keys and values (synthetic context); the end-to-end run prefills its prompts for real.
+Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from
+the fallback figures of an earlier measurement on this pool.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GEMMA_2B = dict(vocab_size=256000, hidden_size=2048, intermediate_size=16384, num_hidden_layers=18,
+                num_attention_heads=8, num_key_value_heads=1, head_dim=256, rms_norm_eps=1e-6, rope_theta=10000.0,
+                max_position_embeddings=8192, tie_word_embeddings=True)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]), "source": "measured"}
+        except (ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __enter__(self):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.proc.wait()
+        self.file.close()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            with open(self.file.name) as f:
+                for line in f:
+                    parts = [p.strip() for p in line.split(",")]
+                    if len(parts) < 6 or not parts[0].isdigit():
+                        continue
+                    sm.append(int(parts[0]))
+                    mx.append(int(parts[1]))
+                    reasons.update(n for n, v in zip(names, parts[2:6]) if v.lower().startswith("active"))
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def fill_synthetic_context(runner, caches, context: int, seed: int) -> None:
+    """Give every request `context` cached tokens of random keys and values without running the model."""
+    import torch
+    for rc in caches:
+        runner.cache.reserve([(rc, context)])
+        runner.cache.commit(rc, context)
+    g = torch.Generator(device=runner.device).manual_seed(seed)
+    for group in runner.cache.groups:
+        pages = group.pages
+        flat = pages.view(-1)
+        step = 1 << 26
+        for i in range(0, flat.numel(), step):
+            n = min(step, flat.numel() - i)
+            flat[i:i + n] = torch.randn(n, generator=g, device=runner.device, dtype=torch.float32).to(pages.dtype)
+
+
+def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: int, page_size: int):
+    """Device-timed decode: `steps` steps of `batch` single tokens at contexts context .. context+steps."""
+    import torch
+    from wllm_b200.engine import StepEntry, build_runner
+    from wllm_b200.kernels import ops
+    from wllm_b200.sampling import SamplingParams
+    from wllm_b200.sampling.sampler import Sampler
+    total = context + warmup + steps + 1
+    pages = batch * (-(-total // page_size)) + 1
+    runner = build_runner(model, engine_cfg, num_pages=pages)
+    if engine_cfg.cuda_graphs:
+        runner.enable_graphs()
+    sampler = Sampler(runner.device)
+    caches = [runner.cache.open(i) for i in range(batch)]
+    fill_synthetic_context(runner, caches, context, seed=3)
+    g = torch.Generator().manual_seed(5)
+    tokens = torch.randint(0, model.plan.vocab_size, (warmup + steps, batch), generator=g).tolist()
+    greedy = [SamplingParams()] * batch
+    zeros, empty = [0] * batch, [set()] * batch
+
+    def one(i):
+        logits = runner.step([StepEntry(rc, [tokens[i][b]], [0]) for b, rc in enumerate(caches)])
+        sampler.launch(logits, greedy, zeros, zeros, empty)
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches0, graph0 = ops.launches, runner.graph_launches
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler() as clocks:
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        end.record()
+        torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = (ops.launches - launches0) + (runner.graph_launches - graph0)
+    kv_bytes = batch * (context + warmup + steps / 2.0) * runner.cache.bytes_per_token()
+    for rc in caches:
+        runner.cache.close(rc)
+    del runner
+    torch.cuda.empty_cache()
+    return ms, launches, kv_bytes, clocks.summary()
+
+
+def prefill_run(model, engine_cfg, tokens: int, page_size: int, repeats: int = 3):
+    import torch
+    from wllm_b200.engine import StepEntry, build_runner
+    runner = build_runner(model, engine_cfg, num_pages=-(-tokens // page_size) + 1)
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, model.plan.vocab_size, (tokens,), generator=g).tolist()
+    times = []
+    for i in range(repeats + 1):
+        rc = runner.cache.open(i)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(rc, prompt, [tokens - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        if i > 0:
+            times.append(start.elapsed_time(end))
+        runner.cache.close(rc)
+    del runner
+    torch.cuda.empty_cache()
+    return min(times)
+
+
+def prefill_flops(cfg, layers: int, tokens: int) -> float:
+    H, I, nq, nkv, hd, V = (cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads,
+                            cfg.head_dim, cfg.vocab_size)
+    per_layer = 2.0 * tokens * ((nq + 2 * nkv) * hd * H + nq * hd * H + 3 * I * H) + 2.0 * nq * hd * tokens * tokens
+    return layers * per_layer + 2.0 * V * H
+
+
+def e2e_run(cfg, args, page_size: int):
+    """The same decode through LLM.add_request / LLM.step: real prefill of the prompts, then timed steps."""
+    import torch
+    from wllm_b200 import LLM, SamplingParams
+    # requests that finish their prompt early decode while the others still prefill: leave room for that
+    prefill_steps = args.batch * (-(-args.context // 2048)) + 1
+    context = min(args.context, cfg.max_position_embeddings - (args.warmup + args.steps) - prefill_steps - 4)
+    total = context + args.warmup + args.steps + prefill_steps + 4
+    llm = LLM(None, config=cfg, random_seed=1, dtype="bfloat16", block_size=page_size,
+              num_blocks=args.batch * (-(-total // page_size)) + 1, chunked_prefill_tokens=2048,
+              max_num_seqs=max(args.batch, 8), cuda_graphs=not args.no_graphs)
+    g = torch.Generator().manual_seed(11)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + prefill_steps + 2, ignore_eos=True)
+    for _ in range(args.batch):
+        llm.add_request(torch.randint(0, cfg.vocab_size, (context,), generator=g).tolist(), sp)
+    while any(r.status.value != "running" for r in llm.scheduler.live) or llm.scheduler.waiting:
+        llm.step()
+    for _ in range(args.warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        got = llm.step()
+        assert len(got) == args.batch
+    torch.cuda.synchronize()
+    sec = (time.perf_counter() - t0) / args.steps
+    h2d = llm.runner.h2d_bytes + llm.sampler.h2d_bytes
+    d2h = llm.sampler.d2h_bytes
+    del llm
+    torch.cuda.empty_cache()
+    return args.batch / sec, h2d, d2h
+
+
+def reference_arm() -> int:
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference's GPU decode path JIT-builds its kernel with an MSVC-only compiler flag "
+                      "(src/wllm/kernels/paged_attention.py:16-20) and does not build under gcc/Linux; "
+                      "its checkpoints come from a hub that this box cannot reach"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=None, help="cached tokens per request when the timed steps begin")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--page-size", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from wllm_b200.config import EngineConfig, GemmaConfig
+    from wllm_b200.engine import build_model
+
+    raw = dict(GEMMA_2B, architectures=["GemmaForCausalLM"])
+    layers_full = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = GemmaConfig.from_dict(raw)
+    if args.context is None:
+        args.context = cfg.max_position_embeddings - (args.warmup + args.steps) - 2
+    ps = args.page_size
+    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=64, cuda_graphs=not args.no_graphs)
+    pk = peaks()
+    model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
+    weight_bytes = model.weight_bytes()
+
+    ms, launches, kv_bytes, clocks = decode_run(model, engine_cfg, args.batch, args.context, args.steps, args.warmup, ps)
+    value = args.batch / (ms / 1e3)
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _, _ = decode_run(model, engine_cfg, b, args.context, min(args.steps, 32), args.warmup, ps)
+            points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
+
+    T = 2048
+    pre_ms = prefill_run(model, engine_cfg, T, ps)
+    flops = prefill_flops(cfg, cfg.num_hidden_layers, T)
+    prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    del model
+    torch.cuda.empty_cache()
+
+    e2e = None
+    if not args.no_e2e:
+        ev, h2d, d2h = e2e_run(cfg, args, ps)
+        e2e = {"value": round(ev, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    line = {
+        "metric": "Gemma-2B decode tok/s @ batch 1/8/64; prefill tok/s @ 2048 tokens",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights N(0,0.02), random token ids, random cached keys/values)",
+        "impl": "ours",
+        "config": {"model": "gemma-2b", "layers": cfg.num_hidden_layers, "layers_full": layers_full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": args.batch, "seq_len": args.context, "page_size": ps, "prefill_tokens": T,
+                   "cuda_graphs": not args.no_graphs, "parallelism": "single-gpu",
+                   "l2": "inputs larger than L2 (weights %.2f GB read every step)" % (weight_bytes / 1e9),
+                   "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

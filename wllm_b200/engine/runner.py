@@ -22,6 +22,7 @@ import torch
 from ..cache import CacheManager, RequestCache
 from ..kernels import ops
 from .model import ComposedModel
+from .staging import PinnedRing
 
 
 @dataclass
@@ -61,10 +62,14 @@ class ModelRunner:
             raise RuntimeError("the model's weights are not loaded")
         self.model, self.cache, self.device = model, cache, torch.device(device)
         self._arena: dict = {}
-        self._pinned = None
+        self._ring = PinnedRing(self.device)
         self._meta = None
         self.steps = 0
         self.tokens_run = 0
+        self.h2d_bytes = 0
+        self._graphs_on = False
+        self._graphs: dict = {}        # (requests, table width) -> captured decode step
+        self.graph_launches = 0        # kernel launches replayed from graphs so far
 
     def workspace(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -78,13 +83,13 @@ class ModelRunner:
         return buf[:n].view(shape)
 
     # -- batch building --------------------------------------------------------------
-    def _build(self, entries: list) -> StepContext:
+    def _build(self, entries: list, table_width: int | None = None) -> StepContext:
         cache, ps = self.cache, self.cache.page_size
         G, R = len(cache.groups), len(entries)
         lens = [len(e.tokens) for e in entries]
         N = sum(lens)
         M = sum(len(e.want) for e in entries)
-        P = max(1, max(len(t) for e in entries for t in e.cache.tables) if G else 1)
+        P = table_width or max(1, max(len(t) for e in entries for t in e.cache.tables) if G else 1)
 
         def pad(n):
             return (n + 3) & ~3
@@ -118,13 +123,11 @@ class ModelRunner:
             start += n
         view("want_rows")[:] = wants
 
-        if self._pinned is None or self._pinned.numel() < total:
-            cap = max(total, 4096)
-            self._pinned = torch.empty(cap, dtype=torch.int32).pin_memory() if self.device.type == "cuda" \
-                else torch.empty(cap, dtype=torch.int32)
+        if self._meta is None or self._meta.numel() < total:
+            cap = max(total, 4096, 2 * (self._meta.numel() if self._meta is not None else 0))
+            self._graphs.clear()      # captured steps point into the old index buffer
             self._meta = torch.empty(cap, dtype=torch.int32, device=self.device)
-        self._pinned[:total].copy_(torch.from_numpy(host))
-        self._meta[:total].copy_(self._pinned[:total], non_blocking=True)
+        self._ring.send(host, self._meta)
         self.h2d_bytes = total * 4
 
         ctx = StepContext(self)
@@ -164,6 +167,46 @@ class ModelRunner:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.cache.request_id!r}: wanted place {w} outside its {n} tokens")
 
+    # -- captured decode steps -------------------------------------------------------------
+    def enable_graphs(self) -> None:
+        """Replay a captured CUDA graph for steps in which every request brings one token and
+        wants its logits (a decode step).  One graph per (number of requests, table width);
+        the index arrays live at fixed device addresses and are rewritten before each replay.
+        The reference captures its decode step in batch-size buckets the same way
+        (src/wllm/engine/cuda_graph_decoder.py:34-178)."""
+        self._graphs_on = True
+
+    def _graphable(self, entries: list) -> bool:
+        return self._graphs_on and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def _forward_graph(self, entries: list) -> torch.Tensor:
+        widest = max(1, max(len(t) for e in entries for t in e.cache.tables))
+        width = 8
+        while width < widest:
+            width *= 2
+        key = (len(entries), width)
+        ctx = self._build(entries, table_width=width)
+        rec = self._graphs.get(key)
+        if rec is None:
+            arena, saved = {}, self._arena
+            self._arena = arena
+            try:
+                self.model.forward(ctx)                  # loads kernels and library handles outside the capture
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                before = ops.launches
+                with torch.cuda.graph(graph):
+                    logits = self.model.forward(ctx)
+                rec = {"graph": graph, "logits": logits, "arena": arena, "launches": ops.launches - before,
+                       "meta": self._meta}
+                ops.launches = before
+            finally:
+                self._arena = saved
+            self._graphs[key] = rec
+        rec["graph"].replay()
+        self.graph_launches += rec["launches"]
+        return rec["logits"]
+
     # -- the step ----------------------------------------------------------------------
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -173,8 +216,12 @@ class ModelRunner:
         self._validate(entries)
         self.cache.reserve([(e.cache, len(e.tokens)) for e in entries])   # all or nothing
         try:
-            ctx = self._build(entries)
-            logits = self.model.forward(ctx)
+            if self._graphable(entries):
+                logits = self._forward_graph(entries)
+                ctx = None
+            else:
+                ctx = self._build(entries)
+                logits = self.model.forward(ctx)
         except BaseException:
             for e in entries:          # a failed step holds no pages beyond its committed tokens
                 self.cache.cancel_reservation(e.cache)
@@ -182,5 +229,5 @@ class ModelRunner:
         for e in entries:
             self.cache.commit(e.cache, len(e.tokens))
         self.steps += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits

@@ -112,10 +112,10 @@ class Scheduler:
     def _may_admit(self, r: Request, taken_now: int) -> bool:
         if len(self.live) >= self.max_num_seqs:
             return False
-        free = min(self.cache.free_pages(), default=1 << 30) - taken_now
-        if self.admission == "worst_case":
+        free = min(self.cache.free_pages(), default=1 << 30)
+        if self.admission == "worst_case":   # the pledge covers the pages this step is about to take
             return self._pages(min(r.worst_case_tokens, self.max_model_len)) <= free - self._pledged()
-        return self._pages(r.num_tokens) <= free
+        return self._pages(r.num_tokens) <= free - taken_now
 
     def _preempt_youngest(self) -> Request:
         victim = self.live.pop()

@@ -14,22 +14,35 @@ import torch
 
 from ..kernels import ops
 from ..kernels.build import load_family
+from ..engine.staging import PinnedRing
 from .params import SamplingParams
 
 
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
-        self._pinned = self._dev = self._out = self._out_host = None
+        self._ring = PinnedRing(self.device)
+        self._dev = self._out = self._out_host = None
+        self.h2d_bytes = 0
         self.d2h_bytes = 0
 
     def sample(self, logits: torch.Tensor, params: list, counters: list, seeds: list, generated: list):
         """logits [rows, vocab] float32 on the device; params[i]: SamplingParams; counters[i]: index of
         the output token being drawn; seeds[i]: the request's 64-bit seed; generated[i]: its distinct
         generated ids (read only when its repetition penalty is not 1).  Returns (tokens, logprobs) lists."""
-        rows, V = logits.shape
+        rows = logits.shape[0]
         if rows == 0:
             return [], []
+        self.launch(logits, params, counters, seeds, generated)
+        self._out_host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes = 8 * rows
+        out = self._out_host[:2 * rows].numpy()
+        return out[:rows].tolist(), out[rows:].view(np.float32).tolist()
+
+    def launch(self, logits: torch.Tensor, params: list, counters: list, seeds: list, generated: list):
+        """Enqueue the sampling of all rows; tokens [rows] int32 stay on the device (returned view)."""
+        rows, V = logits.shape
         if logits.dtype != torch.float32 or logits.stride(1) != 1:
             raise ops.KernelError("sampling needs float32 logits with unit stride along the vocabulary")
         gen_lists = [sorted(g) if p.repetition_penalty != 1.0 else [] for p, g in zip(params, generated)]
@@ -51,16 +64,13 @@ class Sampler:
         host[8 * rows:9 * rows + 1] = offsets
         if n_gen:
             host[9 * rows + 1:] = np.concatenate([np.asarray(g, dtype=np.int32) for g in gen_lists if g])
-        if self._pinned is None or self._pinned.numel() < total:
-            cap = max(total, 8192)
-            self._pinned = torch.empty(cap, dtype=torch.int32).pin_memory()
-            self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        if self._dev is None or self._dev.numel() < total:
+            self._dev = torch.empty(max(total, 8192), dtype=torch.int32, device=self.device)
         if self._out is None or self._out.numel() < 2 * rows:
             cap = max(2 * rows, 1024)
             self._out = torch.empty(cap, dtype=torch.int32, device=self.device)
             self._out_host = torch.empty(cap, dtype=torch.int32).pin_memory()
-        self._pinned[:total].copy_(torch.from_numpy(host))
-        self._dev[:total].copy_(self._pinned[:total], non_blocking=True)
+        self._ring.send(host, self._dev)
         base = self._dev.data_ptr()
 
         def at(i):
@@ -70,8 +80,5 @@ class Sampler:
                                    at(3 * rows), at(4 * rows), at(5 * rows), at(6 * rows), at(7 * rows), at(8 * rows),
                                    at(9 * rows + 1), c_void_p(self._out.data_ptr()),
                                    c_void_p(self._out.data_ptr() + 4 * rows), ops._stream()), "sample")
-        self._out_host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        self.d2h_bytes = 8 * rows
-        out = self._out_host[:2 * rows].numpy()
-        return out[:rows].tolist(), out[rows:].view(np.float32).tolist()
+        self.h2d_bytes = total * 4
+        return self._out[:rows]
