@@ -192,3 +192,61 @@ def test_gemm_f32_is_true_32bit_and_row_invariant(M, N, K):
     # a row of the result does not depend on the other rows of the batch
     alone = ops().gemm_f32(a[M // 2: M // 2 + 1].to(DEV), w.to(DEV)).cpu()
     assert torch.equal(alone[0], got[M // 2])
+
+
+def _mma_inputs(case, seed, spike=True):
+    nq, nkv, hd, ps, ctx_lens, q_lens = case
+    q, kp, vp, treq, pos, table = _paged_case(torch.bfloat16, nq, nkv, hd, ps, ctx_lens, q_lens, seed, spike)
+    table = table.clamp(min=0)
+    starts, s = [], 0
+    for n in q_lens:
+        starts.append(s)
+        s += n
+    meta = [torch.tensor(x, dtype=torch.int32, device=DEV) for x in (starts, q_lens, ctx_lens)]
+    return q, kp, vp, treq, pos, table, meta
+
+
+MMA_CASES = ATTN_CASES + [
+    (8, 1, 256, 64, [1000, 1, 700, 64], [1, 1, 1, 1]),
+    (8, 1, 256, 16, [1030], [1030]),
+    (16, 16, 256, 32, [200, 77], [5, 77]),
+    (4, 2, 96, 16, [500, 333, 2], [1, 300, 2]),
+]
+
+
+@pytest.mark.parametrize("case", MMA_CASES)
+@pytest.mark.parametrize("window", [0, 24])
+@pytest.mark.parametrize("split_keys", [64, 256])
+def test_attention_mma_decode_and_prefill_cover_a_mixed_batch(case, window, split_keys):
+    nq, nkv, hd, ps, ctx_lens, q_lens = case
+    q, kp, vp, treq, pos, table, (starts, qlens, ctxs) = _mma_inputs(case, seed=11, spike=(window == 0))
+    scale = 1.0 / math.sqrt(hd)
+    want = ref.paged_attention(q, torch.empty(q.shape[0], nq * hd, dtype=torch.float64), kp, vp, treq, pos, table,
+                               nq, nkv, hd, ps, window, scale, dtype=torch.float64)
+    got = torch.full((q.shape[0], nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    o = ops()
+    R = len(q_lens)
+    max_splits = -(-max(ctx_lens) // split_keys)
+    scratch = torch.full((o.attention_mma_scratch_floats(R, nq, hd, max_splits),), float("nan"), device=DEV)
+    qd, kd, vd, td = q.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV)
+    decode = any(n == 1 for n in q_lens)
+    if decode:
+        o.attention_mma_decode(qd, got, kd, vd, starts, qlens, ctxs, td, nq, nkv, hd, ps, window, scale, split_keys,
+                               max_splits, scratch)
+    if any(n > 1 for n in q_lens) or not decode:
+        o.attention_mma_prefill(qd, got, kd, vd, starts, qlens, ctxs, td, max(q_lens), nq, nkv, hd, ps, window, scale,
+                                skip_single=decode)
+    torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
+
+
+def test_attention_mma_prefill_alone_serves_single_tokens_too():
+    case = (8, 1, 256, 64, [300, 1, 64], [1, 1, 1])
+    nq, nkv, hd, ps, ctx_lens, q_lens = case
+    q, kp, vp, treq, pos, table, (starts, qlens, ctxs) = _mma_inputs(case, seed=12)
+    scale = 1.0 / math.sqrt(hd)
+    want = ref.paged_attention(q, torch.empty(3, nq * hd, dtype=torch.float64), kp, vp, treq, pos, table, nq, nkv, hd,
+                               ps, 0, scale, dtype=torch.float64)
+    got = torch.full((3, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops().attention_mma_prefill(q.to(DEV), got, kp.to(DEV), vp.to(DEV), starts, qlens, ctxs, table.to(DEV), 1, nq, nkv,
+                                hd, ps, 0, scale, skip_single=False)
+    torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)

@@ -32,6 +32,9 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+SM_COUNT = 148   # B200
+
+
 class StepContext:
     """The batch as the parts see it: index arrays on the device, the cache, scratch buffers."""
 
@@ -44,6 +47,8 @@ class StepContext:
         self.group_slots: list = []
         self.group_tables: list = []
         self.host = None   # the same arrays on the host, for launch decisions
+        self.num_single = self.num_multi = 0     # requests with one token / with several
+        self.max_q_len = self.max_ctx = 0        # bounds that size the attention grids
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         return self.runner.workspace(name, shape, dtype)
@@ -52,8 +57,30 @@ class StepContext:
         return self.cache.slots.tensors[name]
 
     def attention(self, q, out, k_pages, v_pages, group: int, nq: int, nkv: int, hd: int, window: int, scale: float):
-        ops.paged_attention_simt(q, out, k_pages, v_pages, self.token_req, self.positions, self.group_tables[group],
-                                 nq, nkv, hd, self.cache.page_size, window, scale)
+        """Attention of every token of the step over its request's pages.  float32 (and head sizes the
+        tensor-core kernels are not built for): the one-warp-per-row kernel, whose result does not depend
+        on the batch at all.  bfloat16: requests with one token go to the split-key decode kernel, the
+        others to the tiled prefill kernel; both find their requests by q_len on the device."""
+        ps = self.cache.page_size
+        if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
+            ops.paged_attention_simt(q, out, k_pages, v_pages, self.token_req, self.positions,
+                                     self.group_tables[group], nq, nkv, hd, ps, window, scale)
+            return
+        table = self.group_tables[group]
+        decode = self.num_single > 0 and nq // nkv <= 16
+        if decode:
+            R = self.n_requests
+            # enough CTAs for two waves over the SMs, splits of whole 64-key tiles, not below 128 keys
+            keys = -(-self.max_ctx * R * nkv // (2 * SM_COUNT))
+            split_keys = max(128, -(-keys // 64) * 64)
+            max_splits = max(1, -(-self.max_ctx // split_keys))
+            scratch = self.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
+                                  torch.float32)
+            ops.attention_mma_decode(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,
+                                     table, nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch)
+        if self.num_multi > 0 or not decode:
+            ops.attention_mma_prefill(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,
+                                      table, self.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode)
 
 
 class ModelRunner:
@@ -133,6 +160,11 @@ class ModelRunner:
         ctx = StepContext(self)
         ctx.n_tokens, ctx.n_requests, ctx.host = N, R, {k: view(k) for k, _ in sizes}
         ctx.host["max_pages"] = P
+        ctx.num_single = sum(1 for n in lens if n == 1)
+        ctx.num_multi = R - ctx.num_single
+        ctx.max_q_len = max(lens)
+        # under a captured graph the bound must not depend on the batch's contents: the table's reach
+        ctx.max_ctx = table_width * ps if table_width else max(e.cache.num_tokens + n for e, n in zip(entries, lens))
 
         def dev(name):
             o, n = offsets[name]

@@ -129,6 +129,52 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
     return out
 
 
+def mma_head_dim_ok(hd: int) -> bool:
+    """Head sizes the tensor-core attention kernels are built for (one build per size)."""
+    return hd % 16 == 0 and 16 <= hd <= 256
+
+
+def attention_mma_scratch_floats(requests: int, nq: int, hd: int, max_splits: int) -> int:
+    return requests * nq * max_splits * (hd + 2)
+
+
+def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, nq: int, nkv: int,
+                         hd: int, page_size: int, window: int, scale: float, split_keys: int, max_splits: int,
+                         scratch: torch.Tensor) -> None:
+    """bfloat16 attention of the requests that bring one token (csrc/attention_mma.cu, decode)."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, scratch)
+    assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and scratch.dtype == torch.float32
+    R = req_q_len.shape[0]
+    assert scratch.numel() >= attention_mma_scratch_floats(R, nq, hd, max_splits)
+    lib = load_family("attention_mma", {"HEAD_DIM": hd})
+    _check(lib.wllm_attention_mma_decode(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                         _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                                         _ptr(_int32(req_ctx_len, "req_ctx_len")),
+                                         _ptr(_int32(block_table, "block_table")), block_table.shape[1], R, nq, nkv,
+                                         page_size, window, c_float(scale), split_keys, max_splits, _ptr(scratch),
+                                         _stream()), f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
+    global launches
+    launches += 1 if max_splits > 1 else 0    # the merge kernel
+
+
+def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, max_q_len: int,
+                          nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
+                          skip_single: bool) -> None:
+    """bfloat16 attention of the requests that bring several tokens (csrc/attention_mma.cu, prefill)."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table)
+    assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
+    assert k_pages.is_contiguous() and v_pages.is_contiguous()
+    lib = load_family("attention_mma", {"HEAD_DIM": hd})
+    _check(lib.wllm_attention_mma_prefill(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                          _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
+                                          _ptr(_int32(req_ctx_len, "req_ctx_len")),
+                                          _ptr(_int32(block_table, "block_table")), block_table.shape[1],
+                                          req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
+                                          1 if skip_single else 0, _stream()),
+           f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
+
+
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str) -> torch.Tensor:
     """out[n, c] = act(gate_up[n, c]) * gate_up[n, I + c]."""
     _need_cuda(gate_up, out)
@@ -174,4 +220,5 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
 
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
+           "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok",
            "gated_act", "gemm_f32", "linear"]
