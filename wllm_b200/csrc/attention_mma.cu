@@ -10,9 +10,9 @@
 //            `split_keys` keys give a long context to many SMs; each writes its partial
 //            (max, sum, unnormalised output) to scratch and a second kernel merges them
 //            in split order.  A request with a single split writes its output directly.
-//   prefill  one CTA per (request with several new tokens, kv head, tile of 64 rows),
-//            rows = (token, query head of the group); the warps own 16 rows each and walk
-//            all 64-key tiles up to the causal edge.
+//   prefill  one CTA per (request with several new tokens, kv head, tile of 128 rows),
+//            rows = (token, query head of the group); the eight warps own 16 rows each and
+//            walk all 64-key tiles up to the causal edge.
 //
 // Keys and values come straight from the pages through the request's block table
 // ([page][kv_head][slot][head_dim] layout), by 16-byte cp.async into a swizzled,
@@ -68,26 +68,38 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// One 64-key tile of keys or values of kv head `g` into shared memory (all threads).
-__device__ __forceinline__ void load_kv_tile(uint32_t dst, const bf16* __restrict__ pages, const int* __restrict__ table,
-                                             int tile_start, int key_lo, int key_hi, int g, int nkv, int page_size) {
-    for (int idx = threadIdx.x; idx < BN * CPR; idx += NTHREADS) {
+// One 64-key tile of keys AND values of kv head `g` into shared memory (all threads of the CTA).
+// Each warp first reads the tile's page ids (at most four pages of 16 keys) with one load and hands
+// them out by shuffle, so the copies that follow depend on no further load.
+template <int NT>
+__device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, const bf16* __restrict__ k_pages,
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ table,
+                                             int tile_start, int key_lo, int key_hi, int g, int nkv, int page_size,
+                                             int page_shift) {
+    const int lane = threadIdx.x & 31;
+    const int first_page = tile_start >> page_shift;
+    const int last_page = (min(tile_start + BN, key_hi) - 1) >> page_shift;
+    int my_page = 0;
+    if (first_page + lane <= last_page) my_page = table[first_page + lane];
+#pragma unroll
+    for (int it = 0; it < (BN * CPR + NT - 1) / NT; ++it) {
+        const int idx = threadIdx.x + it * NT;
         const int row = idx / CPR, chunk = idx % CPR;
         const int key = tile_start + row;
+        const int page = __shfl_sync(0xffffffffu, my_page, ((key >> page_shift) - first_page) & 31);
+        if (BN * CPR % NT != 0 && idx >= BN * CPR) continue;
         const bool valid = key >= key_lo && key < key_hi;
-        const bf16* src = pages;
-        if (valid) {
-            const int page = table[key / page_size];
-            src = pages + ((size_t)(page * nkv + g) * page_size + key % page_size) * HD + chunk * 8;
-        }
-        cp_async16(dst + swz(row, chunk), src, valid);
+        const size_t off = valid ? ((size_t)(page * nkv + g) * page_size + (key & (page_size - 1))) * HD + chunk * 8 : 0;
+        cp_async16(k_dst + swz(row, chunk), k_pages + off, valid);
+        cp_async16(v_dst + swz(row, chunk), v_pages + off, valid);
     }
 }
 
 // Rows of the query tile: row m of a (request, kv head) is (token m / rep, head g*rep + m % rep).
+template <int NT>
 __device__ __forceinline__ void load_q_tile(uint32_t dst, const bf16* __restrict__ q, int q_stride, int q_start, int q_len,
                                             int row0, int nrows, int g, int rep) {
-    for (int idx = threadIdx.x; idx < nrows * CPR; idx += NTHREADS) {
+    for (int idx = threadIdx.x; idx < nrows * CPR; idx += NT) {
         const int row = idx / CPR, chunk = idx % CPR;
         const int m = row0 + row;
         const bool valid = m < q_len * rep;
@@ -218,23 +230,23 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     init_state(st);
     const bool empty = key_lo >= key_hi;     // the window starts behind this split
     const int t0 = key_lo / BN, t1 = empty ? t0 : (key_hi + BN - 1) / BN;   // tiles [t0, t1)
-    load_q_tile(q_s, q, q_stride, token, 1, 0, 16, g, rep);
+    load_q_tile<NTHREADS>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
+    const int page_shift = 31 - __clz(page_size);
     for (int s = 0; s < DEC_STAGES - 1; ++s) {
-        if (t0 + s < t1) {
-            load_kv_tile(kv_s + (2 * s) * TILE_BYTES, k_pages, table, (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size);
-            load_kv_tile(kv_s + (2 * s + 1) * TILE_BYTES, v_pages, table, (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size);
-        }
+        if (t0 + s < t1)
+            load_kv_tile<NTHREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
+                                   (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
         cp_commit();
     }
-    const int pos_r[2] = {pos, pos}, first_r[2] = {key_lo, key_lo};
+    const int first_r[2] = {key_lo, key_lo};
     for (int t = t0; t < t1; ++t) {
         cp_wait<DEC_STAGES - 2>();
         __syncthreads();
         const int nxt = t + DEC_STAGES - 1;
         if (nxt < t1) {
             const int s = (nxt - t0) % DEC_STAGES;
-            load_kv_tile(kv_s + (2 * s) * TILE_BYTES, k_pages, table, nxt * BN, key_lo, key_hi, g, nkv, page_size);
-            load_kv_tile(kv_s + (2 * s + 1) * TILE_BYTES, v_pages, table, nxt * BN, key_lo, key_hi, g, nkv, page_size);
+            load_kv_tile<NTHREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
+                                   nxt * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
         }
         cp_commit();
         const int s = (t - t0) % DEC_STAGES;
@@ -242,7 +254,6 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
         warp_tile<16>(st, q_s, kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, warp * 16, t * BN, hi_r,
                       first_r, scale2);
     }
-    (void)pos_r;
     cp_wait<0>();
     __syncthreads();
 
@@ -291,36 +302,53 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     }
 }
 
-// merge of the splits: grid (nq, requests), HD threads (rounded up to a warp)
+// merge of the splits: grid (nq, requests).  The splits' weights exp2(m_s - M) are computed once into
+// shared memory; every thread then sums its output columns over the splits in split order.
+constexpr int MERGE_MAX_SPLITS = 256;
 __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* __restrict__ req_q_start,
                              const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len, int nq,
                              int split_keys, int max_splits, const float* __restrict__ part_o,
                              const float* __restrict__ part_ml) {
+    __shared__ float w[MERGE_MAX_SPLITS];
+    __shared__ float inv_l;
     const int head = blockIdx.x, r = blockIdx.y;
     if (req_q_len[r] != 1) return;
     const int num_splits = (req_ctx_len[r] + split_keys - 1) / split_keys;
     if (num_splits <= 1) return;
     const size_t slot0 = ((size_t)r * nq + head) * max_splits;
-    float M = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
-    const float base = M == -INFINITY ? 0.f : M;
-    float L = 0.f;
-    for (int s = 0; s < num_splits; ++s) L += part_ml[(slot0 + s) * 2 + 1] * exp2f(part_ml[(slot0 + s) * 2] - base);
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int s = threadIdx.x; s < num_splits; s += 32) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
+        M = warp_max(M);
+        const float base = M == -INFINITY ? 0.f : M;
+        float L = 0.f;
+        for (int s = threadIdx.x; s < num_splits; s += 32) {
+            const float f = exp2f(part_ml[(slot0 + s) * 2] - base);
+            w[s] = f;
+            L += part_ml[(slot0 + s) * 2 + 1] * f;
+        }
+        L = warp_sum(L);
+        if (threadIdx.x == 0) inv_l = 1.0f / L;
+    }
+    __syncthreads();
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float O = 0.f;
-        for (int s = 0; s < num_splits; ++s) O += part_o[(slot0 + s) * HD + d] * exp2f(part_ml[(slot0 + s) * 2] - base);
-        out[(size_t)req_q_start[r] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
+#pragma unroll 4
+        for (int s = 0; s < num_splits; ++s) O += part_o[(slot0 + s) * HD + d] * w[s];
+        out[(size_t)req_q_start[r] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O * inv_l);
     }
 }
 
 // --------------------------------------------------------------------------------------
 // prefill: grid (row tiles, nkv, requests); heavier (later) row tiles first
 // --------------------------------------------------------------------------------------
-constexpr int BM = NWARPS * 16;
+constexpr int PRE_WARPS = 8;
+constexpr int PRE_THREADS = PRE_WARPS * 32;
+constexpr int BM = PRE_WARPS * 16;
 constexpr int PRE_STAGES = 2;
 constexpr int PRE_SMEM = BM * ROWB + PRE_STAGES * 2 * TILE_BYTES;
 
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(PRE_THREADS)
 prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ req_q_start,
                const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len, const int* __restrict__ block_table,
@@ -354,12 +382,12 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     }
     RowState st;
     init_state(st);
-    load_q_tile(q_s, q, q_stride, q_start, q_len, row0, BM, g, rep);
+    const int page_shift = 31 - __clz(page_size);
+    load_q_tile<PRE_THREADS>(q_s, q, q_stride, q_start, q_len, row0, BM, g, rep);
     for (int s = 0; s < PRE_STAGES - 1; ++s) {
-        if (t0 + s < t1) {
-            load_kv_tile(kv_s + (2 * s) * TILE_BYTES, k_pages, table, (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size);
-            load_kv_tile(kv_s + (2 * s + 1) * TILE_BYTES, v_pages, table, (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size);
-        }
+        if (t0 + s < t1)
+            load_kv_tile<PRE_THREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
+                                      (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
         cp_commit();
     }
     for (int t = t0; t < t1; ++t) {
@@ -368,8 +396,8 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         const int nxt = t + PRE_STAGES - 1;
         if (nxt < t1) {
             const int s = (nxt - t0) % PRE_STAGES;
-            load_kv_tile(kv_s + (2 * s) * TILE_BYTES, k_pages, table, nxt * BN, key_lo, key_hi, g, nkv, page_size);
-            load_kv_tile(kv_s + (2 * s + 1) * TILE_BYTES, v_pages, table, nxt * BN, key_lo, key_hi, g, nkv, page_size);
+            load_kv_tile<PRE_THREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
+                                      nxt * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
         }
         cp_commit();
         const int s = (t - t0) % PRE_STAGES;
@@ -378,7 +406,6 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         if (t * BN <= warp_hi && row0 + warp * 16 < rows)
             warp_tile<BN>(st, q_s + warp * 16 * ROWB, kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, 0,
                           t * BN, pos_r, first_r, scale2);
-        __syncthreads();
     }
     cp_wait<0>();
 #pragma unroll
@@ -425,7 +452,8 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     if (requests <= 0) return WLLM_OK;
     const int bad = check_common(q, q_stride, out, out_stride, nq, nkv, page_size);
     if (bad) return bad;
-    if (nq / nkv > 16 || split_keys < BN || split_keys % BN != 0 || max_splits < 1) return WLLM_BAD_SIZE;
+    if (nq / nkv > 16 || split_keys < BN || split_keys % BN != 0 || max_splits < 1 || max_splits > MERGE_MAX_SPLITS)
+        return WLLM_BAD_SIZE;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
@@ -440,7 +468,7 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
         max_splits, part_o, part_ml);
     int status = wllm_launch_status();
     if (status || max_splits == 1) return status;
-    merge_kernel<<<dim3(nq, requests), HD >= 128 ? 128 : 64, 0, stream>>>(
+    merge_kernel<<<dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream>>>(
         (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits, part_o, part_ml);
     return wllm_launch_status();
 }
@@ -461,7 +489,7 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
         configured = true;
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
-    prefill_kernel<<<dim3(tiles, nkv, requests), NTHREADS, PRE_SMEM, stream>>>(
+    prefill_kernel<<<dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, req_q_start,
         req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single);
     return wllm_launch_status();

@@ -8,7 +8,30 @@
 // of squares is reduced in a fixed order that depends on nothing but the row.
 #include "common.cuh"
 
-template <typename TD, typename TW, typename TO>
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<uint32_t*>(&a);
+    t.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
+// VEC = 4: rows whose width is a multiple of 4 are read and written four elements at a time.
+template <typename TD, typename TW, typename TO, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const TW* __restrict__ w,
                                float eps, float offset, TO* __restrict__ out, const int* __restrict__ rows, int H) {
     __shared__ float scratch[32];
@@ -18,32 +41,44 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
     const TD* d = delta ? delta + (size_t)row * H : nullptr;
     const bool write_back = (d != nullptr) && (rows == nullptr);
     float ss = 0.f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float v = r[c];
-        if (d) v += to_f32(d[c]);
-        ss += v * v;
+    for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC == 4) { load4(r + c, v); if (d) load4(d + c, dv); }
+        else { v[0] = r[c]; if (d) dv[0] = to_f32(d[c]); }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { v[k] += dv[k]; ss += v[k] * v[k]; }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TO* o = out + (size_t)i * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float v = r[c];
-        if (d) v += to_f32(d[c]);
-        if (write_back) r[c] = v;
-        o[c] = from_f32<TO>((v * inv) * (offset + to_f32(w[c])));
+    for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC == 4) { load4(r + c, v); if (d) load4(d + c, dv); load4(w + c, wv); }
+        else { v[0] = r[c]; if (d) dv[0] = to_f32(d[c]); wv[0] = to_f32(w[c]); }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] += dv[k];
+        if (write_back) {
+            if (VEC == 4) store4(r + c, v); else r[c] = v[0];
+        }
+        float y[4];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) y[k] = (v[k] * inv) * (offset + wv[k]);
+        if (VEC == 4) store4(o + c, y); else o[c] = from_f32<TO>(y[0]);
     }
 }
 
 template <typename TD, typename TW>
 static int launch_out(float* resid, const void* delta, const void* w, float eps, float offset, void* out, int out_dtype,
                       const int* rows, int n, int H, cudaStream_t stream) {
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-    if (out_dtype == WLLM_BF16)
-        rmsnorm_kernel<TD, TW, bf16><<<n, threads, 0, stream>>>(resid, (const TD*)delta, (const TW*)w, eps, offset, (bf16*)out, rows, H);
-    else if (out_dtype == WLLM_F32)
-        rmsnorm_kernel<TD, TW, float><<<n, threads, 0, stream>>>(resid, (const TD*)delta, (const TW*)w, eps, offset, (float*)out, rows, H);
-    else
-        return WLLM_BAD_DTYPE;
+    const bool vec = H % 4 == 0 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
+                     ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    const int per = vec ? 4 : 1;
+    const int threads = H / per >= 1024 ? 512 : (H / per >= 256 ? 256 : 128);
+#define GO(TO, V) rmsnorm_kernel<TD, TW, TO, V><<<n, threads, 0, stream>>>(resid, (const TD*)delta, (const TW*)w, eps, offset, (TO*)out, rows, H)
+    if (out_dtype == WLLM_BF16) { if (vec) GO(bf16, 4); else GO(bf16, 1); }
+    else if (out_dtype == WLLM_F32) { if (vec) GO(float, 4); else GO(float, 1); }
+    else return WLLM_BAD_DTYPE;
+#undef GO
     return wllm_launch_status();
 }
 

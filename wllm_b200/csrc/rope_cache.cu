@@ -12,49 +12,39 @@
 // page * page_size + slot_in_page.
 #include "common.cuh"
 
+// grid (token, head): head < nq rotates a query head in place, nq <= head < nq + nkv rotates a key head
+// into its page, the rest copy a value head into its page.
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
                                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
                                      T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int hd,
                                      int rot_dim, int page_size) {
-    const int t = blockIdx.x;
-    T* row = qkv + (size_t)t * row_stride;
-    const float pos = (float)positions[t];
+    const int t = blockIdx.x, h = blockIdx.y;
+    T* x = qkv + (size_t)t * row_stride + (size_t)h * hd;
     const int slot = slots ? slots[t] : -1;
-    const int half = rot_dim >> 1;
-    size_t page_base = 0;
-    int off = 0;
-    if (slot >= 0) {
-        page_base = (size_t)(slot / page_size) * nkv;
-        off = slot % page_size;
+    T* dst = nullptr;
+    if (h >= nq) {
+        if (slot < 0) return;
+        const int kvh = h < nq + nkv ? h - nq : h - nq - nkv;
+        T* pages = h < nq + nkv ? k_pages : v_pages;
+        dst = pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * hd;
     }
+    if (h >= nq + nkv) {
+        for (int c = threadIdx.x; c < hd; c += blockDim.x) dst[c] = x[c];
+        return;
+    }
+    const float pos = (float)positions[t];
+    const int half = rot_dim >> 1;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         float s, c;
         sincosf(pos * inv_freq[j], &s, &c);
-        for (int h = 0; h < nq + nkv; ++h) {
-            T* x = row + (size_t)h * hd;
-            const float x1 = to_f32(x[j]), x2 = to_f32(x[j + half]);
-            const T y1 = from_f32<T>(x1 * c - x2 * s), y2 = from_f32<T>(x2 * c + x1 * s);
-            if (h < nq) {
-                x[j] = y1;
-                x[j + half] = y2;
-            } else if (slot >= 0) {
-                T* dst = k_pages + ((page_base + (h - nq)) * page_size + off) * hd;
-                dst[j] = y1;
-                dst[j + half] = y2;
-            }
-        }
+        const float x1 = to_f32(x[j]), x2 = to_f32(x[j + half]);
+        const T y1 = from_f32<T>(x1 * c - x2 * s), y2 = from_f32<T>(x2 * c + x1 * s);
+        if (dst) { dst[j] = y1; dst[j + half] = y2; }
+        else { x[j] = y1; x[j + half] = y2; }
     }
-    if (slot < 0) return;
-    // unrotated tail of the keys
-    for (int idx = threadIdx.x; idx < nkv * (hd - rot_dim); idx += blockDim.x) {
-        const int h = idx / (hd - rot_dim), c = rot_dim + idx % (hd - rot_dim);
-        k_pages[((page_base + h) * page_size + off) * hd + c] = row[(size_t)(nq + h) * hd + c];
-    }
-    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-        const int h = idx / hd, c = idx % hd;
-        v_pages[((page_base + h) * page_size + off) * hd + c] = row[(size_t)(nq + nkv + h) * hd + c];
-    }
+    if (dst)
+        for (int c = rot_dim + threadIdx.x; c < hd; c += blockDim.x) dst[c] = x[c];
 }
 
 WLLM_API int wllm_rope_kv_write(void* qkv, int dtype, int row_stride, const int* positions, const int* slots,
@@ -63,11 +53,12 @@ WLLM_API int wllm_rope_kv_write(void* qkv, int dtype, int row_stride, const int*
     if (n <= 0) return WLLM_OK;
     if (hd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv <= 0) return WLLM_BAD_SIZE;
     const int threads = hd >= 256 ? 128 : (hd >= 128 ? 64 : 32);
+    const dim3 grid(n, nq + 2 * nkv);
     if (dtype == WLLM_BF16)
-        rope_kv_write_kernel<bf16><<<n, threads, 0, stream>>>((bf16*)qkv, row_stride, positions, slots, inv_freq,
+        rope_kv_write_kernel<bf16><<<grid, threads, 0, stream>>>((bf16*)qkv, row_stride, positions, slots, inv_freq,
                                                                (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd, rot_dim, page_size);
     else if (dtype == WLLM_F32)
-        rope_kv_write_kernel<float><<<n, threads, 0, stream>>>((float*)qkv, row_stride, positions, slots, inv_freq,
+        rope_kv_write_kernel<float><<<grid, threads, 0, stream>>>((float*)qkv, row_stride, positions, slots, inv_freq,
                                                                 (float*)k_pages, (float*)v_pages, nq, nkv, hd, rot_dim, page_size);
     else
         return WLLM_BAD_DTYPE;

@@ -70,9 +70,10 @@ class StepContext:
         decode = self.num_single > 0 and nq // nkv <= 16
         if decode:
             R = self.n_requests
-            # enough CTAs for two waves over the SMs, splits of whole 64-key tiles, not below 128 keys
-            keys = -(-self.max_ctx * R * nkv // (2 * SM_COUNT))
-            split_keys = max(128, -(-keys // 64) * 64)
+            # one CTA fits on an SM: split every (request, kv head) so that all CTAs run in one wave,
+            # in whole 64-key tiles and not below 128 keys
+            per_head = max(1, SM_COUNT // (R * nkv))
+            split_keys = max(128, -(-(-(-self.max_ctx // per_head)) // 64) * 64)
             max_splits = max(1, -(-self.max_ctx // split_keys))
             scratch = self.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
                                   torch.float32)
