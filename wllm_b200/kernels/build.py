@@ -60,13 +60,25 @@ def _build_dir() -> str:
     raise KernelBuildError(f"no writable folder for compiled kernels (tried {first} and the temporary directory)")
 
 
-def _headers() -> list[str]:
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+def _deps(source: str) -> list[str]:
+    """The source and every file of this folder it includes, directly or not."""
+    seen, todo = [], [source]
+    while todo:
+        path = todo.pop()
+        if path in seen or not os.path.isfile(path):
+            continue
+        seen.append(path)
+        with open(path, "r", encoding="utf-8") as f:
+            for line in f:
+                line = line.strip()
+                if line.startswith("#include \""):
+                    todo.append(os.path.join(CSRC, line.split('"')[1]))
+    return [source] + sorted(p for p in seen if p != source)
 
 
 def _key(source: str, flags: list[str]) -> str:
     h = hashlib.sha256()
-    for path in [source] + _headers():
+    for path in _deps(source):
         with open(path, "rb") as f:
             h.update(os.path.basename(path).encode() + b"\0" + f.read() + b"\0")
     h.update(" ".join(ARCH_FLAGS + BASE_FLAGS + flags).encode())
