@@ -211,11 +211,74 @@ def e2e_run(cfg, args, page_size: int):
     return args.batch / sec, h2d, d2h
 
 
-def reference_arm() -> int:
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference's GPU decode path JIT-builds its kernel with an MSVC-only compiler flag "
-                      "(src/wllm/kernels/paged_attention.py:16-20) and does not build under gcc/Linux; "
-                      "its checkpoints come from a hub that this box cannot reach"}))
+def reference_arm(args) -> int:
+    """The unmodified reference from baseline/_ref through its own classes: GemmaForCausalLM with random
+    weights, KVCacheManager, Scheduler (src/wllm/engine/scheduler.py), the same batch and context.  Its
+    decode step needs its own CUDA kernel, which it builds at first use; where that build fails the arm
+    says so and exits 0."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:400]}))
+        return 0
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "wllm")):
+        return unavailable("the reference is not installed under baseline/_ref (pip install --no-index --no-deps "
+                           "--target baseline/_ref /root/reference)")
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from wllm.engine.kv_cache import KVCacheManager
+        from wllm.engine.scheduler import Scheduler
+        from wllm.engine.sequence import Sequence
+        from wllm.kernels.paged_attention import _get_ext
+        from wllm.models.config import ModelConfig
+        from wllm.models.gemma import GemmaForCausalLM
+    except Exception as e:   # noqa: BLE001
+        return unavailable(f"the reference does not import here: {type(e).__name__}: {e}")
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device")
+    try:
+        _get_ext()           # the reference's own JIT build of csrc/paged_attention.cu
+    except Exception as e:   # noqa: BLE001
+        first = str(e).strip().splitlines()[0] if str(e).strip() else type(e).__name__
+        return unavailable("the reference's CUDA decode kernel does not build on this box (it passes the MSVC-only "
+                           f"flag /Zc:preprocessor, src/wllm/kernels/paged_attention.py:16-20): {first}")
+    c = GEMMA_2B
+    cfg = ModelConfig(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], intermediate_size=c["intermediate_size"],
+                      num_hidden_layers=args.layers or c["num_hidden_layers"], num_attention_heads=c["num_attention_heads"],
+                      num_key_value_heads=c["num_key_value_heads"], rms_norm_eps=c["rms_norm_eps"],
+                      rope_theta=c["rope_theta"], max_position_embeddings=c["max_position_embeddings"],
+                      tie_word_embeddings=True, attention_bias=False, explicit_head_dim=c["head_dim"])
+    torch.manual_seed(1)
+    model = GemmaForCausalLM(cfg)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.normal_(0, 0.02)
+    model = model.to(device="cuda", dtype=torch.bfloat16).eval()
+    context = args.context or c["max_position_embeddings"] - (args.warmup + args.steps) - 2
+    blocks = args.batch * (-(-(context + args.warmup + args.steps + 2) // 16)) + 1
+    cache = KVCacheManager(cfg.num_hidden_layers, blocks, 16, cfg.num_key_value_heads, cfg.head_dim, device="cuda")
+    sched = Scheduler(model, cache, max_prefill_tokens_per_step=2048)
+    g = torch.Generator().manual_seed(11)
+    for i in range(args.batch):
+        sched.add_request(Sequence(seq_id=i, prompt_token_ids=torch.randint(0, cfg.vocab_size, (context,), generator=g).tolist(),
+                                   max_new_tokens=args.warmup + args.steps + 64))
+    while sched.waiting or any(s.status.value != "running" for s in sched.running):
+        sched.step()
+    for _ in range(args.warmup):
+        sched.step()
+    torch.cuda.synchronize()
+    with ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            sched.step()
+        torch.cuda.synchronize()
+        sec = (time.perf_counter() - t0) / args.steps
+    print(json.dumps({"metric": "Gemma-2B decode tok/s @ batch 1/8/64; prefill tok/s @ 2048 tokens", "impl": "reference",
+                      "value": round(args.batch / sec, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 4), "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"model": "gemma-2b", "layers": cfg.num_hidden_layers, "global_batch": args.batch,
+                                 "seq_len": context, "page_size": 16}, "clocks": clocks.summary()}))
     return 0
 
 
@@ -233,13 +296,12 @@ def main() -> int:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
-        return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
-
+    if args.impl == "reference":
+        return reference_arm(args)
     import torch
     from wllm_b200.config import EngineConfig, GemmaConfig
     from wllm_b200.engine import build_model
