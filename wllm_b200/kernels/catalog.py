@@ -16,6 +16,7 @@ FAMILIES = {
     "sampling": [{}],
     # tensor-core attention is built per head size; others are built when a model first asks
     "attention_mma": [{"HEAD_DIM": 256}, {"HEAD_DIM": 32}, {"HEAD_DIM": 48}],
+    "attention_decode_static": [{"HEAD_DIM": 256}],
 }
 
 
