@@ -1,0 +1,354 @@
+// bfloat16 matrix product on the fifth-generation tensor cores:
+//     C[M, N] = A[M, K] * W[N, K]^T        (both operands K-major, 32-bit accumulation in TMEM)
+//
+// One persistent CTA per SM walks 128 x 256 output tiles.  Roles by warp:
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a 128 x 64 tile
+//               of A and two 128 x 64 tiles of W per stage into a four-stage ring in shared memory;
+//   warp 1      allocates the 512 columns of tensor memory (two 128 x 256 fp32 accumulators); one lane
+//               issues tcgen05.mma (M 128, N 256, K 16) on shared-memory descriptors and frees each
+//               stage with tcgen05.commit;
+//   warps 2-5   read a finished accumulator with tcgen05.ld (each warp its own 32 lanes), apply the
+//               epilogue and store, while the next tile's products fill the other accumulator.
+// Epilogues: bfloat16 C; 32-bit C (logits); or the gated feed-forward activation, for which the two
+// W tiles of a stage are rows n..n+127 of the gate matrix and of the up matrix (W = [gate; up]), so
+// that act(gate) * up leaves the kernel and the [M, 2I] intermediate is never written.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT failed polls the waiting role records a code
+// in `status`, stops, and the CTA leaves through the common exit, where tensor memory is freed.
+// Rows of A or W outside the matrices are zero-filled by the TMA unit, so any M and N are taken; K and
+// the row pitches must be multiples of 8 elements (16-byte TMA strides).
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_HALF_BYTES = 128 * BK * 2, B_BYTES = 2 * B_HALF_BYTES;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+constexpr int SMEM_BYTES = RING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3 };
+
+// status codes written by a role that gave up waiting
+enum { GAVE_UP_PRODUCER = 11, GAVE_UP_MMA = 12, GAVE_UP_EPILOGUE = 13 };
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// true when the phase with the given parity has completed; false after WAIT_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups of
+// eight rows 1024 bytes apart.  Fields: start address >> 4 in bits 0-13, leading byte offset >> 4 in
+// 16-29 (unused with swizzle, set to 1), stride byte offset >> 4 in 32-45, version 1 in 46-47, layout 2
+// (128-byte swizzle) in 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: fp32 accumulator (bits 4-5 = 1), bf16 A and B (bits 7-9 and 10-12 = 1), both
+// K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ float epi_gelu(float x) {
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float epi_silu(float x) { return x / (1.0f + expf(-x)); }
+
+template <int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
+               int ldc, int M, int N, int K, int up_row_offset, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    // ring at a 1024-byte boundary (swizzle atoms), barriers behind it
+    const uint32_t ring = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = ring + RING_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t tmem_slot = tempty0 + 16;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_addr(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    const int n_cols = GATED ? N / 2 : N;                       // columns of the output
+    const int tile_n = GATED ? 128 : BN;                        // output columns per tile
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (n_cols + tile_n - 1) / tile_n;
+    const int num_tiles = tiles_m * tiles_n, kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * tile_n;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
+                    const uint32_t a_dst = ring + stage * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * stage;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
+                    tma_load_2d(b_dst, &map_w, bar, kb * BK, n0);
+                    tma_load_2d(b_dst + B_HALF_BYTES, &map_w, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + 128);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) atomicExch(status, GAVE_UP_PRODUCER);
+            // Loads still in flight land in this CTA's shared memory: stay until every stage that was
+            // filled has been consumed (its `empty` phase completes), or the limit passes.
+            for (int s = 0; s < STAGES; ++s) {
+                if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) break;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), IDESC,
+                               (kb > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * stage);          // the stage is free once these products are done
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(tfull0 + 8 * acc);        // the accumulator is complete
+            }
+            if (!ok) atomicExch(status, GAVE_UP_MMA);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5, each its own quarter of the 128 lanes ----------------
+        const int quarter = warp & 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * tile_n;
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < tile_n; c0 += 32) {
+                uint32_t v[32];
+                float f[32];
+                tc_ld32(t_row + c0, v);
+                if (GATED) {
+                    uint32_t u[32];
+                    tc_ld32(t_row + 128 + c0, u);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __uint_as_float(v[i]);
+                        f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : epi_silu(g)) * __uint_as_float(u[i]);
+                    }
+                } else {
+                    tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+                }
+                if (row < M) {
+                    const int col = n0 + c0;
+                    if (EPI == EPI_F32) {
+                        float* dst = reinterpret_cast<float*>(c) + (size_t)row * ldc + col;
+                        if (col + 32 <= n_cols && (ldc & 3) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4)
+                                *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col + i < n_cols) dst[i] = f[i];
+                        }
+                    } else {
+                        bf16* dst = reinterpret_cast<bf16*>(c) + (size_t)row * ldc + col;
+                        if (col + 32 <= n_cols && (ldc & 7) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 o;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]), p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]), p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+                                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(dst + i) = o;
+                            }
+                        } else {
+                            for (int i = 0; i < 32; ++i)
+                                if (col + i < n_cols) dst[i] = __float2bfloat16_rn(f[i]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);   // this warp has drained its quarter
+        }
+        if (!ok && lane == 0) atomicExch(status, GAVE_UP_EPILOGUE);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side: tensor maps (cached by what they describe) and the launch
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, ld;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 10007u) ^ ((size_t)k.ld << 7);
+    }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static std::mutex g_maps_mutex;
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with row pitch `ld`, boxes of 128 rows x 64 columns.
+static int tensor_map(const void* ptr, int rows, int cols, int ld, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_maps_mutex);
+    const MapKey key{ptr, rows, cols, ld};
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) { *out = it->second; return WLLM_OK; }
+    EncodeTiled enc = encoder();
+    if (!enc) return 6;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 2000 + (int)r;
+    if (g_maps.size() > 4096) g_maps.clear();
+    g_maps[key] = m;
+    *out = m;
+    return WLLM_OK;
+}
+
+template <int EPI>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
+                  int* status, int ctas, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<EPI><<<ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mw, c, ldc, M, N, K, up_off, status);
+    return wllm_launch_status();
+}
+
+// C = A W^T.  epilogue 0: bf16 C [M, N]; 1: fp32 C [M, N]; 2 / 3: W = [gate; up] ([N, K], N even), bf16 C [M, N/2]
+// = gelu_tanh(gate) * up / silu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
+WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
+                               int epilogue, int* status, int max_ctas, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return WLLM_OK;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K) return WLLM_BAD_SIZE;
+    if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15)) return WLLM_BAD_ALIGN;
+    const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU;
+    if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
+    CUtensorMap ma, mw;
+    int r = tensor_map(a, M, K, lda, &ma);
+    if (r) return r;
+    r = tensor_map(w, N, K, ldw, &mw);
+    if (r) return r;
+    const int n_cols = gated ? N / 2 : N, tile_n = gated ? 128 : BN;
+    const int tiles = ((M + BM - 1) / BM) * ((n_cols + tile_n - 1) / tile_n);
+    const int ctas = tiles < max_ctas ? tiles : max_ctas;
+    switch (epilogue) {
+        case EPI_BF16: return launch<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, status, ctas, stream);
+        case EPI_F32: return launch<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, status, ctas, stream);
+        case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, status, ctas, stream);
+        case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, status, ctas, stream);
+    }
+    return WLLM_BAD_SIZE;
+}

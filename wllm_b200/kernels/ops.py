@@ -204,6 +204,50 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
     return out
 
 
+_TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3}
+_tc_status: dict = {}
+SM_COUNT = 148
+
+
+def tc_gemm_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Shapes the tensor-memory GEMM takes: bfloat16, unit inner strides, K and pitches in steps of 8."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.dim() == 2 and w.dim() == 2
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
+                 max_ctas: int = SM_COUNT) -> torch.Tensor:
+    """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
+    'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T))."""
+    _need_cuda(a, w, out)
+    if not tc_gemm_ok(a, w):
+        raise KernelError("gemm_bf16_tc: bfloat16 operands with K and row pitches in steps of 8 elements, 16-byte "
+                          f"aligned; got a{tuple(a.shape)} stride {a.stride()} w{tuple(w.shape)} stride {w.stride()}")
+    M, K = a.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    code = _TC_EPILOGUES[epilogue]
+    cols = N // 2 if code >= 2 else N
+    if out is None:
+        out = torch.empty((M, cols), dtype=torch.float32 if code == 1 else torch.bfloat16, device=a.device)
+    assert out.shape == (M, cols) and out.stride(1) == 1 and out.dtype == (torch.float32 if code == 1 else torch.bfloat16)
+    status = _tc_status.get(a.device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=a.device)
+        _tc_status[a.device] = status
+    lib = load_family("gemm_bf16_tc")
+    _check(lib.wllm_gemm_bf16_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, code,
+                                 _ptr(status), max_ctas, _stream()), f"gemm_bf16_tc({M}x{N}x{K}, {epilogue})")
+    return out
+
+
+def tc_gemm_status(device) -> int:
+    """0, or the code of a role of the tensor-memory GEMM that gave up waiting (synchronises)."""
+    status = _tc_status.get(torch.device(device))
+    return 0 if status is None else int(status.item())
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """a @ w^T in the element type of the operands.
 
@@ -220,5 +264,6 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
 
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
-           "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok",
+           "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok", "gemm_bf16_tc", "tc_gemm_ok",
+           "tc_gemm_status",
            "gated_act", "gemm_f32", "linear"]
