@@ -99,16 +99,21 @@ def gemm_f32(a, w, out=None):
     return out
 
 
-def linear(a, w, out=None):
-    r = (a.float() @ w.float().t()).to(a.dtype)
+def linear(a, w, out=None, f32_out=False):
+    r = a.float() @ w.float().t()
+    r = r if f32_out else r.to(a.dtype)
     if out is None:
         return r
     out.copy_(r)
     return out
 
 
+def gated_linear(a, w_gate_up, act, out, scratch):
+    return gated_act(linear(a, w_gate_up), out, act)
+
+
 def install(monkeypatch):
     """Replace the kernels by these functions (host-logic tests only)."""
     from wllm_b200.kernels import ops
-    for name in ("embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt", "gated_act", "gemm_f32", "linear"):
+    for name in ("embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt", "gated_act", "gemm_f32", "linear", "gated_linear"):
         monkeypatch.setattr(ops, name, globals()[name])

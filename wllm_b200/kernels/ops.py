@@ -248,22 +248,40 @@ def tc_gemm_status(device) -> int:
     return 0 if status is None else int(status.item())
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """a @ w^T in the element type of the operands.
+TC_MIN_ROWS = 65   # below this a step is bound by streaming the weights; see linear()
 
-    float32: this engine's own FMA kernel (no reduced-precision matrix mode can
-    reach it).  bfloat16: the vendor's matrix library with 32-bit accumulation,
-    as the reference engine does for every projection (src/wllm/models/llama.py:95-98).
+
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, f32_out: bool = False) -> torch.Tensor:
+    """a @ w^T.
+
+    float32 operands: this engine's own FMA kernel (no reduced-precision matrix mode can reach it).
+    bfloat16 operands: the tcgen05 / tensor-memory kernel of csrc/gemm_bf16_tc.cu when the shapes allow
+    (K and pitches in steps of 8) and the step has more than a handful of rows; otherwise the vendor's
+    matrix library with 32-bit accumulation, which is where the reference engine sends every projection
+    (src/wllm/models/llama.py:95-98).  `f32_out` asks for 32-bit results from bfloat16 operands (logits).
     """
     if a.dtype == torch.float32:
         return gemm_f32(a, w, out)
     _need_cuda(a, w)
+    if tc_gemm_ok(a, w) and (a.shape[0] >= TC_MIN_ROWS or f32_out):
+        return gemm_bf16_tc(a, w, out, "f32" if f32_out else "bf16")
     global launches
     launches += 1
-    return torch.matmul(a, w.t(), out=out) if out is not None else torch.matmul(a, w.t())
+    r = torch.matmul(a, w.t(), out=out) if out is not None and not f32_out else torch.matmul(a, w.t())
+    return r.float() if f32_out else r
+
+
+def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.Tensor, scratch) -> torch.Tensor:
+    """out[n, I] = act(a @ gate^T) * (a @ up^T) with w_gate_up = [gate; up].  bfloat16 with enough rows: one
+    tensor-memory GEMM whose epilogue applies the activation; otherwise product, then activation kernel
+    (`scratch(shape, dtype)` supplies the [n, 2I] intermediate)."""
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up) and a.shape[0] >= TC_MIN_ROWS:
+        return gemm_bf16_tc(a, w_gate_up, out, act)
+    gu = linear(a, w_gate_up, scratch((a.shape[0], w_gate_up.shape[0]), a.dtype))
+    return gated_act(gu, out, act)
 
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
            "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok", "gemm_bf16_tc", "tc_gemm_ok",
            "tc_gemm_status",
-           "gated_act", "gemm_f32", "linear"]
+           "gated_act", "gemm_f32", "linear", "gated_linear"]

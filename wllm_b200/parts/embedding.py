@@ -57,5 +57,4 @@ class LogitsHead:
     def __call__(self, hidden_rows: torch.Tensor, ctx) -> torch.Tensor:
         if self.weight is None:
             self.weight = self.embedding.table
-        logits = ops.linear(hidden_rows, self.weight)
-        return logits if logits.dtype == torch.float32 else logits.float()
+        return ops.linear(hidden_rows, self.weight, f32_out=True)

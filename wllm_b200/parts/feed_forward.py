@@ -2,8 +2,9 @@
 
 spec options: intermediate_size, activation ('gelu_tanh' for Gemma's GeGLU,
 src/wllm/models/gemma.py:54-62; 'silu'), gate_proj/up_proj/down_proj (checkpoint
-names).  gate and up are stored as one matrix [2 I, hidden] (gate rows first), so one
-product feeds the activation kernel, which evaluates act(gate) * up in 32-bit.
+names).  gate and up are stored as one matrix [2 I, hidden] (gate rows first).  Under
+bfloat16 one tensor-memory GEMM computes both products and applies act(gate) * up in its
+epilogue, in 32-bit on the accumulators; otherwise one product feeds the activation kernel.
 """
 from __future__ import annotations
 
@@ -33,6 +34,6 @@ class GatedDense:
 
     def __call__(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
-        gu = ops.linear(x, self.wgu, ctx.buffer("gate_up", (n, 2 * self.inter), self.model_dtype))
-        h = ops.gated_act(gu, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype), self.activation)
+        h = ops.gated_linear(x, self.wgu, self.activation, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype),
+                             lambda shape, dtype: ctx.buffer("gate_up", shape, dtype))
         return ops.linear(h, self.wd, ctx.buffer("branch", (n, self.hidden_size), self.model_dtype))
