@@ -18,8 +18,13 @@ def embed_gather(ids, table, scale, out):
     return out
 
 
-def rmsnorm(resid, delta, weight, eps, offset, out, rows=None):
-    r = resid if delta is None else resid + delta.float()
+def rmsnorm(resid, delta, weight, eps, offset, out, rows=None, delta_splits=0):
+    if delta is not None and delta_splits:
+        r = resid
+        for part in delta:           # partial sums, added to the row in order
+            r = r + part
+    else:
+        r = resid if delta is None else resid + delta.float()
     if rows is not None:
         r = r[rows.long()]
     elif delta is not None:
@@ -29,7 +34,12 @@ def rmsnorm(resid, delta, weight, eps, offset, out, rows=None):
     return out
 
 
-def rope_kv_write(qkv, positions, slots, inv_freq, k_pages, v_pages, nq, nkv, hd, rot_dim, page_size):
+def rope_kv_write(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages, nq, nkv, hd, rot_dim, page_size, in_splits=0):
+    if in_splits:
+        total = torch.zeros_like(qkv[0])
+        for part in qkv:
+            total = total + part
+        qkv = total
     n = qkv.shape[0]
     x = qkv.float().clone().view(n, nq + 2 * nkv, hd)
     ang = positions.float()[:, None] * inv_freq.float()[None, :]
@@ -39,8 +49,8 @@ def rope_kv_write(qkv, positions, slots, inv_freq, k_pages, v_pages, nq, nkv, hd
     x1, x2 = qk[..., :half].clone(), qk[..., half:rot_dim].clone()
     qk[..., :half] = x1 * cos - x2 * sin
     qk[..., half:rot_dim] = x2 * cos + x1 * sin
-    rounded = x.to(qkv.dtype)
-    qkv[:, : nq * hd] = rounded[:, :nq].reshape(n, -1)   # rotated keys go to the pages only
+    rounded = x.to(q_out.dtype)
+    q_out.copy_(rounded[:, :nq].reshape(n, -1))
     if slots is None:
         return
     for t in range(n):
@@ -108,6 +118,10 @@ def linear(a, w, out=None, f32_out=False):
     return out
 
 
+def project(a, w, buffer):
+    return linear(a, w), 0
+
+
 def gated_linear(a, w_gate_up, act, out, scratch):
     return gated_act(linear(a, w_gate_up), out, act)
 
@@ -115,5 +129,5 @@ def gated_linear(a, w_gate_up, act, out, scratch):
 def install(monkeypatch):
     """Replace the kernels by these functions (host-logic tests only)."""
     from wllm_b200.kernels import ops
-    for name in ("embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt", "gated_act", "gemm_f32", "linear", "gated_linear"):
+    for name in ("embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt", "gated_act", "gemm_f32", "linear", "project", "gated_linear"):
         monkeypatch.setattr(ops, name, globals()[name])

@@ -85,18 +85,44 @@ def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
     inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
     k_ref = torch.zeros(pages, nkv, ps, hd, dtype=dtype)
     v_ref = torch.zeros_like(k_ref)
-    qkv_ref = qkv.clone()
-    ref.rope_kv_write(qkv_ref, positions, slots, inv_freq, k_ref, v_ref, nq, nkv, hd, rot, ps)
-    qkv_dev, k_dev, v_dev = qkv.to(DEV), torch.zeros_like(k_ref, device=DEV), torch.zeros_like(v_ref, device=DEV)
-    ops().rope_kv_write(qkv_dev, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k_dev, v_dev, nq, nkv, hd, rot, ps)
+    q_ref = torch.zeros(n, nq * hd, dtype=dtype)
+    ref.rope_kv_write(qkv, q_ref, positions, slots, inv_freq, k_ref, v_ref, nq, nkv, hd, rot, ps)
+    q_dev, k_dev, v_dev = (torch.zeros_like(t, device=DEV) for t in (q_ref, k_ref, v_ref))
+    ops().rope_kv_write(qkv.to(DEV), q_dev, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k_dev, v_dev, nq, nkv, hd,
+                        rot, ps)
     t = dict(rtol=1e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
-    torch.testing.assert_close(qkv_dev.cpu().float(), qkv_ref.float(), **t)
+    torch.testing.assert_close(q_dev.cpu().float(), q_ref.float(), **t)
     torch.testing.assert_close(k_dev.cpu().float(), k_ref.float(), **t)
     assert torch.equal(v_dev.cpu(), v_ref)
     # a layer that reads another layer's cache rotates q and writes no page
     k2 = torch.zeros_like(k_dev)
-    ops().rope_kv_write(qkv.to(DEV), positions.to(DEV), None, inv_freq.to(DEV), k2, k2, nq, nkv, hd, rot, ps)
+    ops().rope_kv_write(qkv.to(DEV), q_dev, positions.to(DEV), None, inv_freq.to(DEV), k2, k2, nq, nkv, hd, rot, ps)
     assert float(k2.abs().sum()) == 0.0
+    # the row as three float32 partial sums (what a split-K product leaves)
+    parts = torch.randn(3, *qkv.shape, generator=g)
+    whole = (parts[0] + parts[1]) + parts[2]
+    q3, k3, v3 = (torch.zeros_like(t) for t in (q_ref, k_ref, v_ref))
+    ref.rope_kv_write(whole.to(dtype).float() if False else whole, q3, positions, slots, inv_freq, k3, v3, nq, nkv, hd, rot, ps)
+    q3d, k3d, v3d = (torch.zeros_like(t, device=DEV) for t in (q_ref, k_ref, v_ref))
+    ops().rope_kv_write(parts.to(DEV), q3d, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k3d, v3d, nq, nkv, hd, rot,
+                        ps, in_splits=3)
+    torch.testing.assert_close(q3d.cpu().float(), q3.float(), **t)
+    torch.testing.assert_close(k3d.cpu().float(), k3.float(), **t)
+    torch.testing.assert_close(v3d.cpu().float(), v3.float(), **t)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_adds_partial_sums_in_order(dtype):
+    g = torch.Generator().manual_seed(8)
+    n, H = 6, 2048
+    resid, parts = torch.randn(n, H, generator=g), torch.randn(5, n, H, generator=g)
+    w = (torch.randn(H, generator=g) * 0.1).to(dtype)
+    r_ref, out_ref = resid.clone(), torch.empty(n, H, dtype=dtype)
+    ref.rmsnorm(r_ref, parts, w, 1e-6, 1.0, out_ref, delta_splits=5)
+    r_dev, out_dev = resid.to(DEV), torch.empty(n, H, dtype=dtype, device=DEV)
+    ops().rmsnorm(r_dev, parts.to(DEV), w.to(DEV), 1e-6, 1.0, out_dev, delta_splits=5)
+    assert torch.equal(r_dev.cpu(), r_ref)
+    torch.testing.assert_close(out_dev.cpu().float(), out_ref.float(), **tol(dtype))
 
 
 def _paged_case(dtype, nq, nkv, hd, ps, ctx_lens, q_lens, seed, spike=False):

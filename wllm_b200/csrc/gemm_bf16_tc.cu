@@ -3,7 +3,8 @@
 //
 // One persistent CTA per SM walks 128 x 256 output tiles.  Roles by warp:
 //   warp 0      one lane issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a 128 x 64 tile
-//               of A and two 128 x 64 tiles of W per stage into a four-stage ring in shared memory;
+//               of A and two 128 x 64 tiles of W per stage into a ring of four to six stages in shared
+//               memory;
 //   warp 1      allocates the 512 columns of tensor memory (two 128 x 256 fp32 accumulators); one lane
 //               issues tcgen05.mma (M 128, N 256, K 16) on shared-memory descriptors and frees each
 //               stage with tcgen05.commit;
@@ -23,15 +24,29 @@
 #include <mutex>
 #include <unordered_map>
 
-constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_HALF_BYTES = 128 * BK * 2, B_BYTES = 2 * B_HALF_BYTES;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-constexpr int SMEM_BYTES = RING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int B_HALF_BYTES = 128 * BK * 2, B_BYTES = 2 * B_HALF_BYTES;
+// A product of few rows loads only AROWS (32, 64 or 128) rows of A per stage; the tensor core still reads
+// 128 rows from that address, and the rows past AROWS (whatever lies behind in shared memory) only reach
+// accumulator rows that are never stored.  The smaller stage buys a deeper ring: more weight bytes in
+// flight per SM, which is what a step bound by streaming the weights needs.
+template <int AROWS> struct Ring {
+    static constexpr int STAGES = AROWS == 128 ? 4 : (AROWS == 64 ? 5 : 6);
+    static constexpr int A_BYTES = AROWS * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = RING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3 };
+// With k_splits > 1 (32-bit output only) the K range is cut into k_splits parts of whole 64-column
+// blocks; part s of a tile is a work item of its own and writes its partial sum to slab s of C
+// ([k_splits][M][ldc]).  Whoever reads C adds the slabs in order (the norm and rotary kernels do), so the
+// result does not depend on which CTA ran which part.  This is how a step of a few rows keeps every SM
+// streaming weights.  (Letting the CTA that finishes a tile last add the slabs inside this kernel was
+// tried and measured slower: the sum then runs on one SM at the tail of the kernel.)
 
 // status codes written by a role that gave up waiting
 enum { GAVE_UP_PRODUCER = 11, GAVE_UP_MMA = 12, GAVE_UP_EPILOGUE = 13 };
@@ -100,10 +115,12 @@ __device__ __forceinline__ float epi_gelu(float x) {
 }
 __device__ __forceinline__ float epi_silu(float x) { return x / (1.0f + expf(-x)); }
 
-template <int EPI>
+template <int EPI, int AROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
-               int ldc, int M, int N, int K, int up_row_offset, int* __restrict__ status) {
+               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int* __restrict__ status) {
+    constexpr int STAGES = Ring<AROWS>::STAGES, A_BYTES = Ring<AROWS>::A_BYTES, STAGE_BYTES = Ring<AROWS>::STAGE_BYTES;
+    constexpr int RING_BYTES = Ring<AROWS>::RING_BYTES;
     extern __shared__ unsigned char smem_raw[];
     // ring at a 1024-byte boundary (swizzle atoms), barriers behind it
     const uint32_t ring = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -117,7 +134,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int n_cols = GATED ? N / 2 : N;                       // columns of the output
     const int tile_n = GATED ? 128 : BN;                        // output columns per tile
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (n_cols + tile_n - 1) / tile_n;
-    const int num_tiles = tiles_m * tiles_n, kblocks = (K + BK - 1) / BK;
+    const int tiles_mn = tiles_m * tiles_n, num_tiles = tiles_mn * k_splits;
+    const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -140,8 +158,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * tile_n;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int mn = tile % tiles_mn, split = tile / tiles_mn;
+                const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * tile_n;
+                const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
                     if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
                     const uint32_t a_dst = ring + stage * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * stage;
                     mbar_expect_tx(bar, STAGE_BYTES);
@@ -169,14 +189,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + acc * BN;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int split = tile / tiles_mn;
+                const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
                     if (!mbar_wait(full0 + 8 * stage, phase)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
                         tc_mma(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), IDESC,
-                               (kb > 0 || k > 0) ? 1u : 0u);
+                               (kb > kb_lo || k > 0) ? 1u : 0u);
                     tc_commit(empty0 + 8 * stage);          // the stage is free once these products are done
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -191,13 +213,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
             const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-            const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * tile_n;
+            const int mn = tile % tiles_mn, split = tile / tiles_mn;
+            const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
             tc_fence_after();
             const int row = m0 + quarter * 32 + lane;
             const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+            const bool quarter_has_rows = m0 + quarter * 32 < M;     // the same for the whole warp
 #pragma unroll 1
-            for (int c0 = 0; c0 < tile_n; c0 += 32) {
+            for (int c0 = 0; c0 < tile_n && quarter_has_rows; c0 += 32) {
                 uint32_t v[32];
                 float f[32];
                 tc_ld32(t_row + c0, v);
@@ -218,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (row < M) {
                     const int col = n0 + c0;
                     if (EPI == EPI_F32) {
-                        float* dst = reinterpret_cast<float*>(c) + (size_t)row * ldc + col;
+                        float* dst = reinterpret_cast<float*>(c) + ((size_t)split * M + row) * ldc + col;
                         if (col + 32 <= n_cols && (ldc & 3) == 0) {
 #pragma unroll
                             for (int i = 0; i < 32; i += 4)
@@ -280,28 +304,31 @@ static EncodeTiled encoder() {
 }
 
 struct MapKey {
-    const void* ptr; int rows, cols, ld;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld; }
+    const void* ptr; int rows, cols, ld, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
 };
 struct MapKeyHash {
     size_t operator()(const MapKey& k) const {
-        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 10007u) ^ ((size_t)k.ld << 7);
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 10007u) ^
+               ((size_t)k.ld << 7) ^ (size_t)k.box_rows;
     }
 };
 static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
 static std::mutex g_maps_mutex;
 
-// Tensor map of a row-major bf16 matrix [rows, cols] with row pitch `ld`, boxes of 128 rows x 64 columns.
-static int tensor_map(const void* ptr, int rows, int cols, int ld, CUtensorMap* out) {
+// Tensor map of a row-major bf16 matrix [rows, cols] with row pitch `ld`, boxes of box_rows rows x 64 columns.
+static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
     std::lock_guard<std::mutex> lock(g_maps_mutex);
-    const MapKey key{ptr, rows, cols, ld};
+    const MapKey key{ptr, rows, cols, ld, box_rows};
     auto it = g_maps.find(key);
     if (it != g_maps.end()) { *out = it->second; return WLLM_OK; }
     EncodeTiled enc = encoder();
     if (!enc) return 6;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, 128};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     CUtensorMap m;
     const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
@@ -314,41 +341,61 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, CUtensorMap* 
     return WLLM_OK;
 }
 
-template <int EPI>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                  int* status, int ctas, cudaStream_t stream) {
+template <int EPI, int AROWS>
+static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
+                       int k_splits, int* status, int ctas, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, AROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             Ring<AROWS>::SMEM_BYTES);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
-    gemm_tc_kernel<EPI><<<ctas, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mw, c, ldc, M, N, K, up_off, status);
+    gemm_tc_kernel<EPI, AROWS><<<ctas, NUM_THREADS, Ring<AROWS>::SMEM_BYTES, stream>>>(ma, mw, c, ldc, M, N, K, up_off,
+                                                                                      k_splits, status);
     return wllm_launch_status();
+}
+
+static int a_rows_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
+
+template <int EPI>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
+                  int k_splits, int* status, int ctas, cudaStream_t stream) {
+    switch (a_rows_for(M)) {
+        case 32: return launch_rows<EPI, 32>(ma, mw, c, ldc, M, N, K, up_off, k_splits, status, ctas, stream);
+        case 64: return launch_rows<EPI, 64>(ma, mw, c, ldc, M, N, K, up_off, k_splits, status, ctas, stream);
+    }
+    return launch_rows<EPI, 128>(ma, mw, c, ldc, M, N, K, up_off, k_splits, status, ctas, stream);
 }
 
 // C = A W^T.  epilogue 0: bf16 C [M, N]; 1: fp32 C [M, N]; 2 / 3: W = [gate; up] ([N, K], N even), bf16 C [M, N/2]
 // = gelu_tanh(gate) * up / silu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
+// k_splits > 1 needs epilogue 1 and a C of k_splits slabs [M, ldc]; every part must hold at least one block of K.
 WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
-                               int epilogue, int* status, int max_ctas, cudaStream_t stream) {
+                               int epilogue, int k_splits, int* status, int max_ctas, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return WLLM_OK;
+    if (k_splits < 1 || (k_splits > 1 && epilogue != EPI_F32)) return WLLM_BAD_SIZE;
+    {
+        const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
+        if (kb_per * (k_splits - 1) >= kblocks && k_splits > 1) return WLLM_BAD_SIZE;   // an empty part
+    }
     if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K) return WLLM_BAD_SIZE;
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15)) return WLLM_BAD_ALIGN;
     const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU;
     if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
     CUtensorMap ma, mw;
-    int r = tensor_map(a, M, K, lda, &ma);
+    int r = tensor_map(a, M, K, lda, a_rows_for(M), &ma);
     if (r) return r;
-    r = tensor_map(w, N, K, ldw, &mw);
+    r = tensor_map(w, N, K, ldw, 128, &mw);
     if (r) return r;
     const int n_cols = gated ? N / 2 : N, tile_n = gated ? 128 : BN;
-    const int tiles = ((M + BM - 1) / BM) * ((n_cols + tile_n - 1) / tile_n);
+    const int tiles = ((M + BM - 1) / BM) * ((n_cols + tile_n - 1) / tile_n) * k_splits;
     const int ctas = tiles < max_ctas ? tiles : max_ctas;
     switch (epilogue) {
-        case EPI_BF16: return launch<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, status, ctas, stream);
-        case EPI_F32: return launch<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, status, ctas, stream);
-        case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, status, ctas, stream);
-        case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, status, ctas, stream);
+        case EPI_BF16: return launch<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, 1, status, ctas, stream);
+        case EPI_F32: return launch<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, status, ctas, stream);
+        case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, ctas, stream);
+        case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, ctas, stream);
     }
     return WLLM_BAD_SIZE;
 }

@@ -2,6 +2,8 @@
 // output folded in first:
 //     r = resid[row] (+ delta[row]);  resid[row] = r  (when a delta is given);
 //     out[i] = r * (1 / sqrt(mean(r^2) + eps)) * (offset + w)
+// `delta` may come as `delta_splits` partial sums (slabs `delta_split_stride` elements apart, as the
+// split-K matrix product leaves them); they are added in slab order.
 // All arithmetic is 32-bit; `out` is rounded once to the matrix type.  With `rows`
 // the kernel reads row rows[i] and writes row i (the final norm at the places whose
 // logits are wanted) and leaves the residual untouched.  One block per row; the sum
@@ -30,33 +32,87 @@ __device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
     *reinterpret_cast<uint2*>(p) = t;
 }
 
+// v += part 0 + part 1 + ... in that order.  The loads of sixteen parts are issued together (they do not
+// depend on one another); only the additions are in sequence.
+template <typename TD, int VEC>
+__device__ __forceinline__ void add_parts(float (&v)[4], const TD* __restrict__ d, int parts, size_t stride) {
+    for (int sp = 0; sp < parts; sp += 16) {
+        float dv[16][4];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+            dv[u][0] = dv[u][1] = dv[u][2] = dv[u][3] = 0.f;
+            if (sp + u < parts) {
+                if (VEC == 4) load4(d + (size_t)(sp + u) * stride, dv[u]);
+                else dv[u][0] = to_f32(d[(size_t)(sp + u) * stride]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+            if (sp + u < parts) {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) v[k] += dv[u][k];
+            }
+    }
+}
+
 // VEC = 4: rows whose width is a multiple of 4 are read and written four elements at a time.
 template <typename TD, typename TW, typename TO, int VEC>
-__global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const TW* __restrict__ w,
-                               float eps, float offset, TO* __restrict__ out, const int* __restrict__ rows, int H) {
+__global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, int delta_splits,
+                               size_t delta_split_stride, const TW* __restrict__ w, float eps, float offset,
+                               TO* __restrict__ out, const int* __restrict__ rows, int H) {
     __shared__ float scratch[32];
     const int i = blockIdx.x;
     const int row = rows ? rows[i] : i;
     float* r = resid + (size_t)row * H;
     const TD* d = delta ? delta + (size_t)row * H : nullptr;
     const bool write_back = (d != nullptr) && (rows == nullptr);
+    TO* o = out + (size_t)i * H;
+    if (VEC == 4 && H <= (int)blockDim.x * 16) {
+        // the whole row fits in registers (at most four vectors a thread): one pass over memory
+        float v[4][4];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = (threadIdx.x + k * blockDim.x) * 4;
+            v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0.f;
+            if (c < H) {
+                load4(r + c, v[k]);
+                if (d) add_parts<TD, 4>(v[k], d + c, delta_splits, delta_split_stride);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss += v[k][e] * v[k][e];
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = (threadIdx.x + k * blockDim.x) * 4;
+            if (c < H) {
+                float wv[4], y[4];
+                load4(w + c, wv);
+                if (write_back) store4(r + c, v[k]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) y[e] = (v[k][e] * inv) * (offset + wv[e]);
+                store4(o + c, y);
+            }
+        }
+        return;
+    }
     float ss = 0.f;
     for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
-        float v[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f};
-        if (VEC == 4) { load4(r + c, v); if (d) load4(d + c, dv); }
-        else { v[0] = r[c]; if (d) dv[0] = to_f32(d[c]); }
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC == 4) load4(r + c, v); else v[0] = r[c];
+        if (d) add_parts<TD, VEC>(v, d + c, delta_splits, delta_split_stride);
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) { v[k] += dv[k]; ss += v[k] * v[k]; }
+        for (int k = 0; k < VEC; ++k) ss += v[k] * v[k];
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-    TO* o = out + (size_t)i * H;
     for (int c = threadIdx.x * VEC; c < H; c += blockDim.x * VEC) {
-        float v[4] = {0.f, 0.f, 0.f, 0.f}, dv[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
-        if (VEC == 4) { load4(r + c, v); if (d) load4(d + c, dv); load4(w + c, wv); }
-        else { v[0] = r[c]; if (d) dv[0] = to_f32(d[c]); wv[0] = to_f32(w[c]); }
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) v[k] += dv[k];
+        float v[4] = {0.f, 0.f, 0.f, 0.f}, wv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC == 4) { load4(r + c, v); load4(w + c, wv); }
+        else { v[0] = r[c]; wv[0] = to_f32(w[c]); }
+        if (d) add_parts<TD, VEC>(v, d + c, delta_splits, delta_split_stride);
         if (write_back) {
             if (VEC == 4) store4(r + c, v); else r[c] = v[0];
         }
@@ -68,13 +124,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
 }
 
 template <typename TD, typename TW>
-static int launch_out(float* resid, const void* delta, const void* w, float eps, float offset, void* out, int out_dtype,
-                      const int* rows, int n, int H, cudaStream_t stream) {
+static int launch_out(float* resid, const void* delta, int delta_splits, size_t delta_split_stride, const void* w, float eps,
+                      float offset, void* out, int out_dtype, const int* rows, int n, int H, cudaStream_t stream) {
     const bool vec = H % 4 == 0 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
-                     ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+                     ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0 && delta_split_stride % 4 == 0;
     const int per = vec ? 4 : 1;
     const int threads = H / per >= 1024 ? 512 : (H / per >= 256 ? 256 : 128);
-#define GO(TO, V) rmsnorm_kernel<TD, TW, TO, V><<<n, threads, 0, stream>>>(resid, (const TD*)delta, (const TW*)w, eps, offset, (TO*)out, rows, H)
+#define GO(TO, V) rmsnorm_kernel<TD, TW, TO, V><<<n, threads, 0, stream>>>(resid, (const TD*)delta, delta_splits, delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H)
     if (out_dtype == WLLM_BF16) { if (vec) GO(bf16, 4); else GO(bf16, 1); }
     else if (out_dtype == WLLM_F32) { if (vec) GO(float, 4); else GO(float, 1); }
     else return WLLM_BAD_DTYPE;
@@ -82,14 +138,15 @@ static int launch_out(float* resid, const void* delta, const void* w, float eps,
     return wllm_launch_status();
 }
 
-WLLM_API int wllm_rmsnorm(float* resid, const void* delta, int delta_dtype, const void* w, int w_dtype, float eps,
-                          float offset, void* out, int out_dtype, const int* rows, int n, int H, cudaStream_t stream) {
+WLLM_API int wllm_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,
+                          const void* w, int w_dtype, float eps, float offset, void* out, int out_dtype, const int* rows,
+                          int n, int H, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
-    if (H <= 0) return WLLM_BAD_SIZE;
+    if (H <= 0 || delta_splits < 1 || delta_split_stride < 0) return WLLM_BAD_SIZE;
     const bool dbf = delta_dtype == WLLM_BF16, wbf = w_dtype == WLLM_BF16;
     if ((delta_dtype != WLLM_BF16 && delta_dtype != WLLM_F32) || (w_dtype != WLLM_BF16 && w_dtype != WLLM_F32)) return WLLM_BAD_DTYPE;
-    if (dbf && wbf) return launch_out<bf16, bf16>(resid, delta, w, eps, offset, out, out_dtype, rows, n, H, stream);
-    if (dbf && !wbf) return launch_out<bf16, float>(resid, delta, w, eps, offset, out, out_dtype, rows, n, H, stream);
-    if (!dbf && wbf) return launch_out<float, bf16>(resid, delta, w, eps, offset, out, out_dtype, rows, n, H, stream);
-    return launch_out<float, float>(resid, delta, w, eps, offset, out, out_dtype, rows, n, H, stream);
+    if (dbf && wbf) return launch_out<bf16, bf16>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
+    if (dbf && !wbf) return launch_out<bf16, float>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
+    if (!dbf && wbf) return launch_out<float, bf16>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
+    return launch_out<float, float>(resid, delta, delta_splits, (size_t)delta_split_stride, w, eps, offset, out, out_dtype, rows, n, H, stream);
 }

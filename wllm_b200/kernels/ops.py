@@ -80,33 +80,49 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torc
 
 
 def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset: float, out: torch.Tensor,
-            rows=None) -> torch.Tensor:
-    """Fold `delta` into the residual (when given), then norm: see csrc/norm.cu."""
+            rows=None, delta_splits: int = 0) -> torch.Tensor:
+    """Fold `delta` into the residual (when given), then norm: see csrc/norm.cu.  With `delta_splits` = S > 0,
+    `delta` is [S, n, H] float32 partial sums that are added in order."""
     _need_cuda(resid, delta, weight, out, rows)
     H = resid.shape[1]
     n = rows.shape[0] if rows is not None else resid.shape[0]
     assert resid.dtype == torch.float32 and resid.is_contiguous() and out.is_contiguous() and out.shape == (n, H)
     assert weight.shape == (H,) and weight.is_contiguous()
+    split_stride = 0
     if delta is not None:
-        assert delta.shape == resid.shape and delta.is_contiguous()
+        assert delta.is_contiguous()
+        if delta_splits:
+            assert delta.shape == (delta_splits,) + tuple(resid.shape) and delta.dtype == torch.float32
+            split_stride = resid.numel()
+        else:
+            assert delta.shape == resid.shape
     lib = load_family("norm")
-    _check(lib.wllm_rmsnorm(_ptr(resid), _ptr(delta), _dt(delta) if delta is not None else _F32, _ptr(weight),
-                            _dt(weight), c_float(eps), c_float(offset), _ptr(out), _dt(out),
-                            _ptr(_int32(rows, "rows") if rows is not None else None), n, H, _stream()), "rmsnorm")
+    _check(lib.wllm_rmsnorm(_ptr(resid), _ptr(delta), _dt(delta) if delta is not None else _F32, max(1, delta_splits),
+                            ctypes.c_longlong(split_stride), _ptr(weight), _dt(weight), c_float(eps), c_float(offset),
+                            _ptr(out), _dt(out), _ptr(_int32(rows, "rows") if rows is not None else None), n, H,
+                            _stream()), "rmsnorm")
     return out
 
 
-def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor, k_pages, v_pages,
-                  nq: int, nkv: int, hd: int, rot_dim: int, page_size: int) -> None:
-    """Rotate q and k inside the fused rows `qkv` [n, (nq+2nkv)*hd]; write k, v to the pages."""
-    _need_cuda(qkv, positions, slots, inv_freq, k_pages, v_pages)
-    n = qkv.shape[0]
-    assert qkv.stride(1) == 1 and qkv.shape[1] == (nq + 2 * nkv) * hd
+def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
+                  k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, in_splits: int = 0) -> None:
+    """Rotate the q and k heads of the fused rows `qkv` [n, (nq+2nkv)*hd] (or [S, n, ...] float32 partial sums
+    when in_splits = S > 0); rotated q goes to `q_out` [n, nq*hd], rotated k and v to the pages."""
+    _need_cuda(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages)
+    width = (nq + 2 * nkv) * hd
+    if in_splits:
+        assert qkv.dim() == 3 and qkv.shape[0] == in_splits and qkv.is_contiguous() and qkv.dtype == torch.float32
+        n, row_stride, split_stride = qkv.shape[1], qkv.stride(1), qkv.stride(0)
+    else:
+        assert qkv.dim() == 2 and qkv.stride(1) == 1
+        n, row_stride, split_stride = qkv.shape[0], qkv.stride(0), 0
+    assert qkv.shape[-1] == width and q_out.shape == (n, nq * hd) and q_out.stride(1) == 1
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_contiguous()
     if slots is not None:
-        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == qkv.dtype == v_pages.dtype
+        assert k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dtype == q_out.dtype == v_pages.dtype
     lib = load_family("rope_cache")
-    _check(lib.wllm_rope_kv_write(_ptr(qkv), _dt(qkv), qkv.stride(0), _ptr(_int32(positions, "positions")),
+    _check(lib.wllm_rope_kv_write(_ptr(qkv), _dt(qkv), row_stride, max(1, in_splits), ctypes.c_longlong(split_stride),
+                                  _ptr(q_out), _dt(q_out), q_out.stride(0), _ptr(_int32(positions, "positions")),
                                   _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
                                   _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size, _stream()),
            "rope_kv_write")
@@ -216,10 +232,20 @@ def tc_gemm_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def split_plan(M: int, N: int, K: int) -> int:
+    """Parts to cut K into so that a product of few rows still gives every SM a share of the weights."""
+    tiles = -(-M // 128) * -(-N // 256)
+    kblocks = -(-K // 64)
+    wanted = max(1, min(kblocks, SM_COUNT // tiles))
+    per = -(-kblocks // wanted)
+    return -(-kblocks // per)
+
+
 def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
-                 max_ctas: int = SM_COUNT) -> torch.Tensor:
+                 max_ctas: int = SM_COUNT, k_splits: int = 1) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
-    'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T))."""
+    'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
+    k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums."""
     _need_cuda(a, w, out)
     if not tc_gemm_ok(a, w):
         raise KernelError("gemm_bf16_tc: bfloat16 operands with K and row pitches in steps of 8 elements, 16-byte "
@@ -229,16 +255,19 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     assert w.shape[1] == K
     code = _TC_EPILOGUES[epilogue]
     cols = N // 2 if code >= 2 else N
+    shape = (M, cols) if k_splits == 1 else (k_splits, M, cols)
     if out is None:
-        out = torch.empty((M, cols), dtype=torch.float32 if code == 1 else torch.bfloat16, device=a.device)
-    assert out.shape == (M, cols) and out.stride(1) == 1 and out.dtype == (torch.float32 if code == 1 else torch.bfloat16)
+        out = torch.empty(shape, dtype=torch.float32 if code == 1 else torch.bfloat16, device=a.device)
+    assert out.shape == shape and out.stride(-1) == 1 and out.dtype == (torch.float32 if code == 1 else torch.bfloat16)
+    assert k_splits == 1 or (code == 1 and out.is_contiguous())
     status = _tc_status.get(a.device)
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=a.device)
         _tc_status[a.device] = status
     lib = load_family("gemm_bf16_tc")
-    _check(lib.wllm_gemm_bf16_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, code,
-                                 _ptr(status), max_ctas, _stream()), f"gemm_bf16_tc({M}x{N}x{K}, {epilogue})")
+    _check(lib.wllm_gemm_bf16_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
+                                 k_splits, _ptr(status), max_ctas, _stream()),
+           f"gemm_bf16_tc({M}x{N}x{K}, {epilogue}, {k_splits} parts)")
     return out
 
 
@@ -256,8 +285,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, f3
 
     float32 operands: this engine's own FMA kernel (no reduced-precision matrix mode can reach it).
     bfloat16 operands: the tcgen05 / tensor-memory kernel of csrc/gemm_bf16_tc.cu when the shapes allow
-    (K and pitches in steps of 8) and the step has more than a handful of rows; otherwise the vendor's
-    matrix library with 32-bit accumulation, which is where the reference engine sends every projection
+    (K and pitches in steps of 8) and the step has more than a handful of rows (steps of few rows go
+    through project() instead); otherwise the vendor's matrix library with 32-bit accumulation, which is where the reference engine sends every projection
     (src/wllm/models/llama.py:95-98).  `f32_out` asks for 32-bit results from bfloat16 operands (logits).
     """
     if a.dtype == torch.float32:
@@ -271,11 +300,29 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, f3
     return r.float() if f32_out else r
 
 
+def project(a: torch.Tensor, w: torch.Tensor, buffer) -> tuple:
+    """a @ w^T for a layer's projections whose reader can add partial sums itself (the norm and the rotary
+    kernels do).  Returns (tensor, parts).  parts = 0: `tensor` is the plain product [n, N] in the operands'
+    type.  parts = S > 0 (bfloat16 steps of few rows, which are bound by streaming the weights): `tensor`
+    is [S, n, N] float32 partial sums over S parts of K, left by a split-K run of the tensor-memory GEMM in
+    which every SM takes a share.  `buffer(name, shape, dtype)` supplies the output."""
+    n, N = a.shape[0], w.shape[0]
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w) and n < TC_MIN_ROWS:
+        parts = split_plan(n, N, a.shape[1])
+        out = buffer("parts", (parts, n, N), torch.float32)
+        if parts == 1:
+            gemm_bf16_tc(a, w, out[0], "f32")
+        else:
+            gemm_bf16_tc(a, w, out, "f32", k_splits=parts)
+        return out, parts
+    return linear(a, w, buffer("product", (n, N), a.dtype)), 0
+
+
 def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.Tensor, scratch) -> torch.Tensor:
     """out[n, I] = act(a @ gate^T) * (a @ up^T) with w_gate_up = [gate; up].  bfloat16 with enough rows: one
     tensor-memory GEMM whose epilogue applies the activation; otherwise product, then activation kernel
     (`scratch(shape, dtype)` supplies the [n, 2I] intermediate)."""
-    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up) and a.shape[0] >= TC_MIN_ROWS:
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up):
         return gemm_bf16_tc(a, w_gate_up, out, act)
     gu = linear(a, w_gate_up, scratch((a.shape[0], w_gate_up.shape[0]), a.dtype))
     return gated_act(gu, out, act)
@@ -284,4 +331,4 @@ def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
            "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok", "gemm_bf16_tc", "tc_gemm_ok",
            "tc_gemm_status",
-           "gated_act", "gemm_f32", "linear", "gated_linear"]
+           "gated_act", "gemm_f32", "linear", "project", "gated_linear", "split_plan"]

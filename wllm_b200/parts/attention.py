@@ -17,7 +17,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import MIXERS, POSITIONS, CacheRef, KVNeed, ParamSpec
+from .base import MIXERS, POSITIONS, CacheRef, KVNeed, ParamSpec, as_branch
 
 
 @MIXERS.register("attention")
@@ -49,15 +49,15 @@ class PagedAttention:
         self.wo = fetch(n["o_proj"]).contiguous()
         self.position.to(self.wo.device)
 
-    def __call__(self, x: torch.Tensor, ctx, cache: CacheRef) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, ctx, cache: CacheRef):
         n = x.shape[0]
-        qkv = ops.linear(x, self.wqkv, ctx.buffer("qkv", (n, self.wqkv.shape[0]), self.model_dtype))
+        qkv, parts = ops.project(x, self.wqkv, lambda name, shape, dt: ctx.buffer("qkv_" + name, shape, dt))
         group = ctx.cache.groups[cache.group]
         k_pages, v_pages = group.keys(cache.layer), group.values(cache.layer)
-        ops.rope_kv_write(qkv, ctx.positions, ctx.group_slots[cache.group] if cache.writes else None,
+        q = ctx.buffer("q_rotated", (n, self.nq * self.hd), self.model_dtype)
+        ops.rope_kv_write(qkv, q, ctx.positions, ctx.group_slots[cache.group] if cache.writes else None,
                           self.position.inv_freq, k_pages, v_pages, self.nq, self.nkv, self.hd,
-                          self.position.rotary_dim, group.page_size)
+                          self.position.rotary_dim, group.page_size, in_splits=parts)
         attn = ctx.buffer("attn", (n, self.nq * self.hd), self.model_dtype)
-        ctx.attention(qkv[:, : self.nq * self.hd], attn, k_pages, v_pages, cache.group, self.nq, self.nkv, self.hd,
-                      self.window or 0, self.scale)
-        return ops.linear(attn, self.wo, ctx.buffer("branch", (n, self.hidden_size), self.model_dtype))
+        ctx.attention(q, attn, k_pages, v_pages, cache.group, self.nq, self.nkv, self.hd, self.window or 0, self.scale)
+        return as_branch(ops.project(attn, self.wo, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))

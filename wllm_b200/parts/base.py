@@ -81,13 +81,33 @@ class CacheRef:
     state_names: dict | None = None   # mixer's own name -> name in the manager's state slots
 
 
+class Partials:
+    """A branch output still in parts: [parts, n, hidden] float32 partial sums (a split-K product), which the
+    next norm adds in order while it folds them into the residual."""
+
+    def __init__(self, tensor: torch.Tensor):
+        self.tensor, self.parts = tensor, tensor.shape[0]
+
+
+def as_branch(product):
+    """What ops.project returned, as a branch output: a tensor, or Partials."""
+    tensor, parts = product
+    return Partials(tensor) if parts else tensor
+
+
 class Residual:
-    """The residual stream in 32-bit, and the branch output not yet added to it.
-    The next norm folds `pending` in (one kernel), so no separate add is launched."""
+    """The residual stream in 32-bit, and the branch output not yet added to it (a tensor [n, hidden], or
+    `Partials`).  The next norm folds `pending` in (one kernel), so no separate add is launched."""
 
     def __init__(self, stream: torch.Tensor):
         self.stream = stream
-        self.pending: torch.Tensor | None = None
+        self.pending = None
+
+    def pending_args(self) -> tuple:
+        """(delta tensor or None, number of parts) for the norm kernel."""
+        if isinstance(self.pending, Partials):
+            return self.pending.tensor, self.pending.parts
+        return self.pending, 0
 
 
 class Registry(dict):

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import FEED_FORWARDS, ParamSpec
+from .base import FEED_FORWARDS, ParamSpec, as_branch
 
 
 @FEED_FORWARDS.register("gated_dense")
@@ -32,8 +32,8 @@ class GatedDense:
         self.wgu = torch.cat([fetch(n["gate_proj"]), fetch(n["up_proj"])], dim=0).contiguous()
         self.wd = fetch(n["down_proj"]).contiguous()
 
-    def __call__(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, ctx):
         n = x.shape[0]
         h = ops.gated_linear(x, self.wgu, self.activation, ctx.buffer("ffn_act", (n, self.inter), self.model_dtype),
                              lambda shape, dtype: ctx.buffer("gate_up", shape, dtype))
-        return ops.linear(h, self.wd, ctx.buffer("branch", (n, self.hidden_size), self.model_dtype))
+        return as_branch(ops.project(h, self.wd, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))

@@ -31,11 +31,13 @@ class RMSNorm:
 
     def __call__(self, residual: Residual, ctx) -> torch.Tensor:
         out = ctx.buffer("normed", (residual.stream.shape[0], self.hidden_size), self.model_dtype)
-        ops.rmsnorm(residual.stream, residual.pending, self.weight, self.eps, self.offset, out)
+        delta, parts = residual.pending_args()
+        ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, delta_splits=parts)
         residual.pending = None
         return out
 
     def rows(self, residual: Residual, rows: torch.Tensor, ctx) -> torch.Tensor:
         out = torch.empty((rows.shape[0], self.hidden_size), dtype=self.model_dtype, device=rows.device)
-        ops.rmsnorm(residual.stream, residual.pending, self.weight, self.eps, self.offset, out, rows=rows)
+        delta, parts = residual.pending_args()
+        ops.rmsnorm(residual.stream, delta, self.weight, self.eps, self.offset, out, rows=rows, delta_splits=parts)
         return out
