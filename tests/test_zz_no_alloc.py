@@ -39,10 +39,13 @@ def _case(seed, nq, nkv, ps, ctx_lens):
 def _call_static(lib, q, out, k, v, table, meta, nq, nkv, ps, scale, split_keys, max_splits):
     starts, qlens, ctxs = meta
     p = lambda t: c_void_p(t.data_ptr())   # noqa: E731
-    return lib.wllm_attention_mma_decode_static(
-        p(q), q.stride(0), p(out), out.stride(0), p(k), p(v), p(starts), p(qlens), p(ctxs), p(table), table.shape[1],
-        qlens.shape[0], nq, nkv, ps, 0, c_float(scale), split_keys, max_splits,
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)     # stays 0 unless a bounded wait in the kernel ran out
+    rc = lib.wllm_attention_mma_decode_static(
+        p(q), q.stride(0), p(out), out.stride(0), p(k), p(v), ctypes.c_longlong(k.shape[0]), p(starts), p(qlens), p(ctxs),
+        p(table), table.shape[1], qlens.shape[0], nq, nkv, ps, 0, c_float(scale), split_keys, max_splits, p(status),
         c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert int(status.item()) == 0
+    return rc
 
 
 def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():

@@ -34,18 +34,19 @@ WLLM_API long long wllm_attention_mma_decode_static_needs(int requests, int nq, 
 }
 
 WLLM_API int wllm_attention_mma_decode_static(const void* q, int q_stride, void* out, int out_stride,
-                                              const void* k_pages, const void* v_pages, const int* req_q_start,
-                                              const int* req_q_len, const int* req_ctx_len, const int* block_table,
-                                              int max_pages, int requests, int nq, int nkv, int page_size, int window,
-                                              float scale, int split_keys, int max_splits, cudaStream_t stream) {
+                                              const void* k_pages, const void* v_pages, long long pool_pages,
+                                              const int* req_q_start, const int* req_q_len, const int* req_ctx_len,
+                                              const int* block_table, int max_pages, int requests, int nq, int nkv,
+                                              int page_size, int window, float scale, int split_keys, int max_splits,
+                                              int* status, cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
     if (nq <= 0 || max_splits < 1) return WLLM_BAD_SIZE;
     if (wllm_attention_mma_scratch_floats(requests, nq, max_splits) > (long long)WLLM_STATIC_SCRATCH_FLOATS)
         return WLLM_SCRATCH_TOO_SMALL;
     float* scratch = nullptr;
-    const int status = static_scratch(&scratch);
-    if (status != WLLM_OK) return status;
-    return wllm_attention_mma_decode(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len,
+    const int rc = static_scratch(&scratch);
+    if (rc != WLLM_OK) return rc;
+    return wllm_attention_mma_decode(q, q_stride, out, out_stride, k_pages, v_pages, pool_pages, req_q_start, req_q_len,
                                      req_ctx_len, block_table, max_pages, requests, nq, nkv, page_size, window, scale,
-                                     split_keys, max_splits, scratch, stream);
+                                     split_keys, max_splits, scratch, status, stream);
 }

@@ -39,10 +39,10 @@ extern "C" {
 #endif
 
 int wllm_attention_mma_decode_static(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                     const void* v_pages, const int* req_q_start, const int* req_q_len,
-                                     const int* req_ctx_len, const int* block_table, int max_pages, int requests,
-                                     int nq, int nkv, int page_size, int window, float scale, int split_keys,
-                                     int max_splits, cudaStream_t stream);
+                                     const void* v_pages, long long pool_pages, const int* req_q_start,
+                                     const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                     int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                     float scale, int split_keys, int max_splits, int* status, cudaStream_t stream);
 
 /* Floats of the static array that a call with these sizes would use. */
 long long wllm_attention_mma_decode_static_needs(int requests, int nq, int max_splits);

@@ -15,13 +15,21 @@
 //            walk all 64-key tiles up to the causal edge.
 //
 // Keys and values come straight from the pages through the request's block table
-// ([page][kv_head][slot][head_dim] layout), by 16-byte cp.async into a swizzled,
-// multi-stage ring in shared memory; rows outside a request's keys are zero-filled.
+// ([page][kv_head][slot][head_dim] layout) into a swizzled multi-stage ring in shared memory.
+// Head sizes that are multiples of 64: one thread issues TMA box copies (cp.async.bulk.tensor,
+// 128-byte swizzle, 64 columns x up to 64 slots of one page and head per box) that complete on an
+// mbarrier; rows past a request's keys hold whatever the page holds and are masked.  Other head
+// sizes: 16-byte cp.async by all threads, rows outside a request's keys zero-filled.
+// Waits on the mbarriers are bounded; a CTA that gives up records a code in `status` and leaves.
 // Scores, the running maximum and sum and the output accumulate in 32-bit; the
 // exponentials are exp2 of log2(e)-scaled scores.  Which requests each kernel serves is
 // read from q_len on the device (1: decode, more: prefill), so a captured graph stays
 // valid when the batch changes its contents but not its shape.
 #include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<head size>"
@@ -39,9 +47,36 @@ constexpr int NWARPS = 4;
 constexpr int NTHREADS = NWARPS * 32;
 constexpr int TILE_BYTES = BN * ROWB;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr bool USE_TMA = (HD % 64 == 0);
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+enum { GAVE_UP_DECODE = 21, GAVE_UP_PREFILL = 22 };
 
+// Byte offset of 16-byte chunk `chunk` of row `row` in a tile of ROWS rows.  cp.async layout: rows of
+// ROWB bytes, chunks XOR-swizzled inside each 128-byte group.  TMA layout: one sub-tile [ROWS][128 bytes]
+// per 64 columns (what a 128-byte-swizzled box copy writes), the same XOR inside each 128-byte row.
+template <int ROWS>
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    if (USE_TMA) return (uint32_t)((chunk >> 3) * (ROWS * 128) + row * 128 + ((((chunk ^ row) & 7)) << 4));
     return (uint32_t)(row * ROWB + ((((chunk & ~7) | ((chunk ^ row) & 7))) << 4));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -90,13 +125,35 @@ __device__ __forceinline__ void load_kv_tile(uint32_t k_dst, uint32_t v_dst, con
         if (BN * CPR % NT != 0 && idx >= BN * CPR) continue;
         const bool valid = key >= key_lo && key < key_hi;
         const size_t off = valid ? ((size_t)(page * nkv + g) * page_size + (key & (page_size - 1))) * HD + chunk * 8 : 0;
-        cp_async16(k_dst + swz(row, chunk), k_pages + off, valid);
-        cp_async16(v_dst + swz(row, chunk), v_pages + off, valid);
+        cp_async16(k_dst + swz<BN>(row, chunk), k_pages + off, valid);
+        cp_async16(v_dst + swz<BN>(row, chunk), v_pages + off, valid);
+    }
+}
+
+// The same tile by TMA (one thread): per page that the tile touches and per 64 columns, one box of
+// [min(page_size, 64) slots][64 columns] of keys and one of values.  The pool is seen as a matrix of
+// [pages * nkv * page_size rows][HD columns]; a released or unallocated page (< 0) is read as page 0 and masked.
+__device__ __forceinline__ void tma_kv_tile(uint32_t k_dst, uint32_t v_dst, uint32_t bar, const CUtensorMap* k_map,
+                                            const CUtensorMap* v_map, const int* __restrict__ table, int max_pages,
+                                            int tile_start, int g, int nkv, int page_size, int page_shift) {
+    mbar_expect_tx(bar, 2 * TILE_BYTES);
+    const int box_rows = page_size < BN ? page_size : BN;
+    for (int r0 = 0; r0 < BN; r0 += box_rows) {
+        const int key = tile_start + r0;
+        const int index = key >> page_shift;          // the last tile may reach past the request's pages
+        int page = index < max_pages ? table[index] : 0;
+        if (page < 0) page = 0;
+        const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+#pragma unroll
+        for (int cb = 0; cb < HD / 64; ++cb) {
+            tma_load_2d(k_dst + cb * (BN * 128) + r0 * 128, k_map, bar, cb * 64, row);
+            tma_load_2d(v_dst + cb * (BN * 128) + r0 * 128, v_map, bar, cb * 64, row);
+        }
     }
 }
 
 // Rows of the query tile: row m of a (request, kv head) is (token m / rep, head g*rep + m % rep).
-template <int NT>
+template <int NT, int ROWS>
 __device__ __forceinline__ void load_q_tile(uint32_t dst, const bf16* __restrict__ q, int q_stride, int q_start, int q_len,
                                             int row0, int nrows, int g, int rep) {
     for (int idx = threadIdx.x; idx < nrows * CPR; idx += NT) {
@@ -105,7 +162,7 @@ __device__ __forceinline__ void load_q_tile(uint32_t dst, const bf16* __restrict
         const bool valid = m < q_len * rep;
         const bf16* src = q;
         if (valid) src = q + (size_t)(q_start + m / rep) * q_stride + (size_t)(g * rep + m % rep) * HD + chunk * 8;
-        cp_async16(dst + swz(row, chunk), src, valid);
+        cp_async16(dst + swz<ROWS>(row, chunk), src, valid);
     }
 }
 
@@ -118,8 +175,8 @@ struct RowState {
 // One warp: its 16 query rows (at q_rows in shared memory) against NKEYS keys of a tile
 // that start at shared-memory row `key0`; `pos_r[i]`/`first_r[i]` bound the keys each of the
 // thread's two rows may see; `key_base` is the absolute index of tile row 0.
-template <int NKEYS>
-__device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_rows, uint32_t k_tile, uint32_t v_tile, int key0,
+template <int NKEYS, int QROWS>
+__device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_row0, uint32_t k_tile, uint32_t v_tile, int key0,
                                           int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2) {
     constexpr int NT = NKEYS / 8;
     const int lane = threadIdx.x & 31;
@@ -131,11 +188,11 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_rows, uint32_
 #pragma unroll
     for (int kt = 0; kt < KT; ++kt) {
         uint32_t a[4];
-        ldsm4(q_rows + swz(a_row, kt * 2 + a_chunk), a);
+        ldsm4(q_tile + swz<QROWS>(q_row0 + a_row, kt * 2 + a_chunk), a);
 #pragma unroll
         for (int np = 0; np < NT / 2; ++np) {
             uint32_t b[4];
-            ldsm4(k_tile + swz(key0 + np * 16 + b_row, kt * 2 + b_chunk), b);
+            ldsm4(k_tile + swz<BN>(key0 + np * 16 + b_row, kt * 2 + b_chunk), b);
             mma16816(s[2 * np], a, b[0], b[1]);
             mma16816(s[2 * np + 1], a, b[2], b[3]);
         }
@@ -187,7 +244,7 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_rows, uint32_
 #pragma unroll
         for (int np = 0; np < NTO / 2; ++np) {
             uint32_t b[4];
-            ldsm4t(v_tile + swz(key0 + kk * 16 + v_row, np * 2 + v_chunk), b);
+            ldsm4t(v_tile + swz<BN>(key0 + kk * 16 + v_row, np * 2 + v_chunk), b);
             mma16816(st.o[2 * np], p, b[0], b[1]);
             mma16816(st.o[2 * np + 1], p, b[2], b[3]);
         }
@@ -202,18 +259,90 @@ __device__ __forceinline__ void init_state(RowState& st) {
 }
 
 // --------------------------------------------------------------------------------------
+// the tile ring: cp.async groups, or TMA with one "full" mbarrier per stage
+// --------------------------------------------------------------------------------------
+// Both kernels walk tiles t0 .. t1-1 with the same schedule: before tile t is used, every thread waits
+// until it has landed, then the CTA synchronises (so tile t-1's stage is free) and the load of tile
+// t + STAGES - 1 is issued into that stage.
+template <int STAGES, int NT>
+struct TileRing {
+    uint32_t kv_s, bars;          // shared-memory addresses of the stages and of the mbarriers
+    const bf16 *k_pages, *v_pages;
+    const CUtensorMap *k_map, *v_map;
+    const int* table;
+    int max_pages, key_lo, key_hi, g, nkv, page_size, page_shift, t0, t1;
+
+    __device__ __forceinline__ uint32_t k_stage(int s) const { return kv_s + (2 * s) * TILE_BYTES; }
+    __device__ __forceinline__ uint32_t v_stage(int s) const { return kv_s + (2 * s + 1) * TILE_BYTES; }
+
+    __device__ __forceinline__ void init() {
+        if (USE_TMA) {
+            if (threadIdx.x == 0) {
+                for (int s = 0; s < STAGES; ++s) mbar_init(bars + 8 * s, 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            __syncthreads();
+        }
+    }
+    __device__ __forceinline__ void issue(int t) {      // tile t into its stage
+        const int s = (t - t0) % STAGES;
+        if (USE_TMA) {
+            if (threadIdx.x == 0 && t < t1)
+                tma_kv_tile(k_stage(s), v_stage(s), bars + 8 * s, k_map, v_map, table, max_pages, t * BN, g, nkv, page_size,
+                            page_shift);
+        } else {
+            if (t < t1)
+                load_kv_tile<NT>(k_stage(s), v_stage(s), k_pages, v_pages, table, t * BN, key_lo, key_hi, g, nkv, page_size,
+                                 page_shift);
+            cp_commit();
+        }
+    }
+    __device__ __forceinline__ void prologue() {
+        for (int s = 0; s < STAGES - 1; ++s) issue(t0 + s);
+    }
+    // false (for every thread of the CTA alike) if the tile did not arrive within the limit (TMA only)
+    __device__ __forceinline__ bool arrive(int t) {
+        int ok = 1;
+        if (USE_TMA) {
+            const int n = t - t0;
+            ok = mbar_wait(bars + 8 * (n % STAGES), (n / STAGES) & 1) ? 1 : 0;
+        } else {
+            cp_wait<STAGES - 2>();
+        }
+        ok = __syncthreads_and(ok);
+        if (ok) issue(t + STAGES - 1);
+        return ok != 0;
+    }
+    // Nothing of this CTA's copies may be in flight when it leaves.  After a normal run that is so already;
+    // after giving up on tile `failed`, the tiles issued behind it are waited for, again with the limit.
+    __device__ __forceinline__ void drain(int failed) {
+        if (USE_TMA) {
+            for (int t = failed + 1; failed >= 0 && t < min(t1, failed + STAGES - 1); ++t) {
+                const int n = t - t0;
+                if (!mbar_wait(bars + 8 * (n % STAGES), (n / STAGES) & 1)) break;
+            }
+        } else {
+            cp_wait<0>();
+        }
+        __syncthreads();
+    }
+};
+
+// --------------------------------------------------------------------------------------
 // decode: grid (max_splits, nkv, requests)
 // --------------------------------------------------------------------------------------
 constexpr int DEC_STAGES = 3;
-constexpr int DEC_SMEM = 16 * ROWB + DEC_STAGES * 2 * TILE_BYTES;
+constexpr int DEC_SMEM = 1024 + 16 * ROWB + DEC_STAGES * 2 * TILE_BYTES + 64;
 
 __global__ void __launch_bounds__(NTHREADS)
 decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
-              const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ req_q_start,
-              const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len, const int* __restrict__ block_table,
-              int max_pages, int nq, int nkv, int page_size, int window, float scale2, int split_keys, int max_splits,
-              float* __restrict__ part_o, float* __restrict__ part_ml) {
-    extern __shared__ __align__(128) unsigned char smem[];
+              const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+              const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+              const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
+              const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
+              int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
@@ -223,39 +352,40 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     const int key_lo = max(split * split_keys, first), key_hi = min(ctx, (split + 1) * split_keys);
     const int rep = nq / nkv, token = req_q_start[r];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* table = block_table + (size_t)r * max_pages;
-    const uint32_t q_s = smem_u32(smem), kv_s = q_s + 16 * ROWB;
+    // stages at a 1024-byte boundary (swizzle atoms of the box copies), then the query tile, then barriers
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t q_s = base + DEC_STAGES * 2 * TILE_BYTES;
 
     RowState st;
     init_state(st);
     const bool empty = key_lo >= key_hi;     // the window starts behind this split
-    const int t0 = key_lo / BN, t1 = empty ? t0 : (key_hi + BN - 1) / BN;   // tiles [t0, t1)
-    load_q_tile<NTHREADS>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
-    const int page_shift = 31 - __clz(page_size);
-    for (int s = 0; s < DEC_STAGES - 1; ++s) {
-        if (t0 + s < t1)
-            load_kv_tile<NTHREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
-                                   (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
-        cp_commit();
-    }
+    TileRing<DEC_STAGES, NTHREADS> ring;
+    ring.kv_s = base; ring.bars = q_s + 16 * ROWB;
+    ring.k_pages = k_pages; ring.v_pages = v_pages; ring.k_map = &k_map; ring.v_map = &v_map;
+    ring.table = block_table + (size_t)r * max_pages; ring.max_pages = max_pages;
+    ring.key_lo = key_lo; ring.key_hi = key_hi; ring.g = g; ring.nkv = nkv; ring.page_size = page_size;
+    ring.page_shift = 31 - __clz(page_size);
+    ring.t0 = key_lo / BN; ring.t1 = empty ? ring.t0 : (key_hi + BN - 1) / BN;
+    ring.init();
+    load_q_tile<NTHREADS, 16>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
+    if (USE_TMA) cp_commit();
+    ring.prologue();
+    if (USE_TMA) cp_wait<0>();               // the query tile (cp.async); the first arrive() synchronises the CTA
     const int first_r[2] = {key_lo, key_lo};
-    for (int t = t0; t < t1; ++t) {
-        cp_wait<DEC_STAGES - 2>();
-        __syncthreads();
-        const int nxt = t + DEC_STAGES - 1;
-        if (nxt < t1) {
-            const int s = (nxt - t0) % DEC_STAGES;
-            load_kv_tile<NTHREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
-                                   nxt * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
-        }
-        cp_commit();
-        const int s = (t - t0) % DEC_STAGES;
-        const int hi_r[2] = {min(pos, key_hi - 1), min(pos, key_hi - 1)};
-        warp_tile<16>(st, q_s, kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, warp * 16, t * BN, hi_r,
-                      first_r, scale2);
+    const int hi_r[2] = {min(pos, key_hi - 1), min(pos, key_hi - 1)};
+    int t = ring.t0;
+    bool ok = true;
+    for (; t < ring.t1; ++t) {
+        if (!ring.arrive(t)) { ok = false; break; }
+        const int s = (t - ring.t0) % DEC_STAGES;
+        warp_tile<16, 16>(st, q_s, 0, ring.k_stage(s), ring.v_stage(s), warp * 16, t * BN, hi_r, first_r, scale2);
     }
-    cp_wait<0>();
-    __syncthreads();
+    ring.drain(ok ? -1 : t);
+    if (!ok) {
+        if (threadIdx.x == 0) atomicExch(status, GAVE_UP_DECODE);
+        return;
+    }
 
     // merge the four warps through shared memory (the tile ring is free now)
     float* sm_o = reinterpret_cast<float*>(smem);                  // [warp][16][HD]
@@ -283,11 +413,11 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, sm_ml[(w * 16 + row) * 2]);
-        const float base = M == -INFINITY ? 0.f : M;
+        const float mbase = M == -INFINITY ? 0.f : M;
         float L = 0.f, O = 0.f;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) {
-            const float f = exp2f(sm_ml[(w * 16 + row) * 2] - base);
+            const float f = exp2f(sm_ml[(w * 16 + row) * 2] - mbase);
             L += sm_ml[(w * 16 + row) * 2 + 1] * f;
             O += sm_o[(size_t)(w * 16 + row) * HD + d] * f;
         }
@@ -346,14 +476,16 @@ constexpr int PRE_WARPS = 8;
 constexpr int PRE_THREADS = PRE_WARPS * 32;
 constexpr int BM = PRE_WARPS * 16;
 constexpr int PRE_STAGES = 2;
-constexpr int PRE_SMEM = BM * ROWB + PRE_STAGES * 2 * TILE_BYTES;
+constexpr int PRE_SMEM = 1024 + BM * ROWB + PRE_STAGES * 2 * TILE_BYTES + 64;
 
 __global__ void __launch_bounds__(PRE_THREADS)
 prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
-               const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ req_q_start,
-               const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len, const int* __restrict__ block_table,
-               int max_pages, int nq, int nkv, int page_size, int window, float scale2, int skip_single) {
-    extern __shared__ __align__(128) unsigned char smem[];
+               const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+               const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+               const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
+               const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
+               int skip_single, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
     const int g = blockIdx.y, r = blockIdx.z;
     const int q_len = req_q_len[r];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
@@ -363,15 +495,14 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     if (row0 >= rows) return;
     const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;   // position of the request's first new token
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* table = block_table + (size_t)r * max_pages;
-    const uint32_t q_s = smem_u32(smem), kv_s = q_s + BM * ROWB;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = base + PRE_STAGES * 2 * TILE_BYTES;
 
     // keys this CTA needs: from the first row's window start to the last row's position
     const int last_row = min(rows, row0 + BM) - 1;
     const int pos_hi = pos0 + last_row / rep;
     const int pos_lo = pos0 + row0 / rep;
     const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
-    const int t0 = key_lo / BN, t1 = (key_hi + BN - 1) / BN;
 
     int pos_r[2], first_r[2];
 #pragma unroll
@@ -382,32 +513,33 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     }
     RowState st;
     init_state(st);
-    const int page_shift = 31 - __clz(page_size);
-    load_q_tile<PRE_THREADS>(q_s, q, q_stride, q_start, q_len, row0, BM, g, rep);
-    for (int s = 0; s < PRE_STAGES - 1; ++s) {
-        if (t0 + s < t1)
-            load_kv_tile<PRE_THREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
-                                      (t0 + s) * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
-        cp_commit();
-    }
-    for (int t = t0; t < t1; ++t) {
-        cp_wait<PRE_STAGES - 2>();
-        __syncthreads();
-        const int nxt = t + PRE_STAGES - 1;
-        if (nxt < t1) {
-            const int s = (nxt - t0) % PRE_STAGES;
-            load_kv_tile<PRE_THREADS>(kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, k_pages, v_pages, table,
-                                      nxt * BN, key_lo, key_hi, g, nkv, page_size, page_shift);
-        }
-        cp_commit();
-        const int s = (t - t0) % PRE_STAGES;
+    TileRing<PRE_STAGES, PRE_THREADS> ring;
+    ring.kv_s = base; ring.bars = q_s + BM * ROWB;
+    ring.k_pages = k_pages; ring.v_pages = v_pages; ring.k_map = &k_map; ring.v_map = &v_map;
+    ring.table = block_table + (size_t)r * max_pages; ring.max_pages = max_pages;
+    ring.key_lo = key_lo; ring.key_hi = key_hi; ring.g = g; ring.nkv = nkv; ring.page_size = page_size;
+    ring.page_shift = 31 - __clz(page_size);
+    ring.t0 = key_lo / BN; ring.t1 = (key_hi + BN - 1) / BN;
+    ring.init();
+    load_q_tile<PRE_THREADS, BM>(q_s, q, q_stride, q_start, q_len, row0, BM, g, rep);
+    if (USE_TMA) cp_commit();
+    ring.prologue();
+    if (USE_TMA) cp_wait<0>();
+    int t = ring.t0;
+    bool ok = true;
+    for (; t < ring.t1; ++t) {
+        if (!ring.arrive(t)) { ok = false; break; }
+        const int s = (t - ring.t0) % PRE_STAGES;
         // a warp whose rows all end before this tile has nothing to add
         const int warp_hi = pos0 + min(rows - 1, row0 + warp * 16 + 15) / rep;
         if (t * BN <= warp_hi && row0 + warp * 16 < rows)
-            warp_tile<BN>(st, q_s + warp * 16 * ROWB, kv_s + (2 * s) * TILE_BYTES, kv_s + (2 * s + 1) * TILE_BYTES, 0,
-                          t * BN, pos_r, first_r, scale2);
+            warp_tile<BN, BM>(st, q_s, warp * 16, ring.k_stage(s), ring.v_stage(s), 0, t * BN, pos_r, first_r, scale2);
     }
-    cp_wait<0>();
+    ring.drain(ok ? -1 : t);
+    if (!ok) {
+        if (threadIdx.x == 0) atomicExch(status, GAVE_UP_PREFILL);
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
@@ -428,8 +560,56 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
 }
 
 // --------------------------------------------------------------------------------------
-// entry points
+// host side: tensor maps over the pools (cached by pointer and shape), entry points
 // --------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+struct PoolKey {
+    const void* ptr; long long rows; int box_rows;
+    bool operator==(const PoolKey& o) const { return ptr == o.ptr && rows == o.rows && box_rows == o.box_rows; }
+};
+struct PoolKeyHash {
+    size_t operator()(const PoolKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)(k.rows * 31 + k.box_rows); }
+};
+static std::unordered_map<PoolKey, CUtensorMap, PoolKeyHash> g_pool_maps;
+static std::mutex g_pool_mutex;
+
+// A pool [pages][nkv][page_size][HD] as a matrix of rows x HD; boxes of box_rows x 64 columns, 128-byte swizzle.
+static int pool_map(const void* ptr, long long rows, int box_rows, CUtensorMap* out) {
+    if (!USE_TMA) { memset(out, 0, sizeof(*out)); return WLLM_OK; }
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    const PoolKey key{ptr, rows, box_rows};
+    auto it = g_pool_maps.find(key);
+    if (it != g_pool_maps.end()) { *out = it->second; return WLLM_OK; }
+    EncodeTiled enc = encoder();
+    if (!enc) return 6;
+    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return 2000 + (int)r;
+    if (g_pool_maps.size() > 4096) g_pool_maps.clear();
+    g_pool_maps[key] = m;
+    *out = m;
+    return WLLM_OK;
+}
+
 WLLM_API int wllm_attention_mma_head_dim() { return HD; }
 
 // Floats of scratch the decode path needs for `requests` requests: partial outputs and (max, sum) pairs.
@@ -437,23 +617,36 @@ WLLM_API long long wllm_attention_mma_scratch_floats(int requests, int nq, int m
     return (long long)requests * nq * max_splits * (HD + 2);
 }
 
-static int check_common(const void* q, int q_stride, const void* out, int out_stride, int nq, int nkv, int page_size) {
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size < 16 || (page_size & (page_size - 1))) return WLLM_BAD_SIZE;
-    if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3)) return WLLM_BAD_ALIGN;
+static int check_common(const void* q, int q_stride, const void* out, int out_stride, const void* k_pages,
+                        const void* v_pages, int nq, int nkv, int page_size, long long pool_pages) {
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size < 16 || (page_size & (page_size - 1)) || pool_pages < 1)
+        return WLLM_BAD_SIZE;
+    if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) ||
+        ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        return WLLM_BAD_ALIGN;
     return WLLM_OK;
 }
 
-// Tokens of requests with q_len == 1.  `scratch` holds wllm_attention_mma_scratch_floats(...) floats.
+// Tokens of requests with q_len == 1.  `scratch` holds wllm_attention_mma_scratch_floats(...) floats;
+// `pool_pages` is the number of pages of k_pages / v_pages; `status` is a device int that stays 0 unless
+// a CTA gave up waiting for a tile.
 WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                       const void* v_pages, const int* req_q_start, const int* req_q_len,
-                                       const int* req_ctx_len, const int* block_table, int max_pages, int requests,
-                                       int nq, int nkv, int page_size, int window, float scale, int split_keys,
-                                       int max_splits, float* scratch, cudaStream_t stream) {
+                                       const void* v_pages, long long pool_pages, const int* req_q_start,
+                                       const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                       int max_pages, int requests, int nq, int nkv, int page_size, int window,
+                                       float scale, int split_keys, int max_splits, float* scratch, int* status,
+                                       cudaStream_t stream) {
     if (requests <= 0) return WLLM_OK;
-    const int bad = check_common(q, q_stride, out, out_stride, nq, nkv, page_size);
+    const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
     if (nq / nkv > 16 || split_keys < BN || split_keys % BN != 0 || max_splits < 1 || max_splits > MERGE_MAX_SPLITS)
         return WLLM_BAD_SIZE;
+    CUtensorMap km, vm;
+    const long long rows = pool_pages * nkv * page_size;
+    int r = pool_map(k_pages, rows, page_size < BN ? page_size : BN, &km);
+    if (r) return r;
+    r = pool_map(v_pages, rows, page_size < BN ? page_size : BN, &vm);
+    if (r) return r;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
@@ -463,11 +656,11 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)requests * nq * max_splits * HD;
     decode_kernel<<<dim3(max_splits, nkv, requests), NTHREADS, DEC_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, req_q_start,
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm, req_q_start,
         req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys,
-        max_splits, part_o, part_ml);
-    int status = wllm_launch_status();
-    if (status || max_splits == 1) return status;
+        max_splits, part_o, part_ml, status);
+    int st = wllm_launch_status();
+    if (st || max_splits == 1) return st;
     merge_kernel<<<dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream>>>(
         (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits, part_o, part_ml);
     return wllm_launch_status();
@@ -475,13 +668,19 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
 
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
 WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                        const void* v_pages, const int* req_q_start, const int* req_q_len,
-                                        const int* req_ctx_len, const int* block_table, int max_pages, int requests,
-                                        int max_q_len, int nq, int nkv, int page_size, int window, float scale,
-                                        int skip_single, cudaStream_t stream) {
+                                        const void* v_pages, long long pool_pages, const int* req_q_start,
+                                        const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                                        int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
+                                        int window, float scale, int skip_single, int* status, cudaStream_t stream) {
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
-    const int bad = check_common(q, q_stride, out, out_stride, nq, nkv, page_size);
+    const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
+    CUtensorMap km, vm;
+    const long long rows = pool_pages * nkv * page_size;
+    int r = pool_map(k_pages, rows, page_size < BN ? page_size : BN, &km);
+    if (r) return r;
+    r = pool_map(v_pages, rows, page_size < BN ? page_size : BN, &vm);
+    if (r) return r;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM);
@@ -490,7 +689,7 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
     prefill_kernel<<<dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, req_q_start,
-        req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single);
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm, req_q_start,
+        req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
     return wllm_launch_status();
 }

@@ -36,6 +36,13 @@ __device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
 // depend on one another); only the additions are in sequence.
 template <typename TD, int VEC>
 __device__ __forceinline__ void add_parts(float (&v)[4], const TD* __restrict__ d, int parts, size_t stride) {
+    if (parts == 1) {      // the common case: one tensor to add
+        float dv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (VEC == 4) load4(d, dv); else dv[0] = to_f32(d[0]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] += dv[k];
+        return;
+    }
     for (int sp = 0; sp < parts; sp += 16) {
         float dv[16][4];
 #pragma unroll

@@ -33,6 +33,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
         dst = pages + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * hd;
     }
     auto in = [&](int c) {     // part 0 + part 1 + ... in order; sixteen loads are in flight at a time
+        if (in_splits == 1) return to_f32(x[c]);
         float v = 0.f;
         for (int sp = 0; sp < in_splits; sp += 16) {
             float part[16];

@@ -145,6 +145,15 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
     return out
 
 
+def _status_word(device) -> torch.Tensor:
+    """One int32 per device that stays 0 unless a kernel's bounded wait ran out (see kernel_status)."""
+    status = _tc_status.get(device)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        _tc_status[device] = status
+    return status
+
+
 def mma_head_dim_ok(hd: int) -> bool:
     """Head sizes the tensor-core attention kernels are built for (one build per size)."""
     return hd % 16 == 0 and 16 <= hd <= 256
@@ -165,11 +174,13 @@ def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_c
     assert scratch.numel() >= attention_mma_scratch_floats(R, nq, hd, max_splits)
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
     _check(lib.wllm_attention_mma_decode(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                         ctypes.c_longlong(k_pages.shape[0]),
                                          _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                          _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                          _ptr(_int32(block_table, "block_table")), block_table.shape[1], R, nq, nkv,
                                          page_size, window, c_float(scale), split_keys, max_splits, _ptr(scratch),
-                                         _stream()), f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
+                                         _ptr(_status_word(q.device)), _stream()),
+           f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
     global launches
     launches += 1 if max_splits > 1 else 0    # the merge kernel
 
@@ -183,11 +194,12 @@ def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
     _check(lib.wllm_attention_mma_prefill(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                          ctypes.c_longlong(k_pages.shape[0]),
                                           _ptr(_int32(req_q_start, "req_q_start")), _ptr(_int32(req_q_len, "req_q_len")),
                                           _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                           _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                           req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
-                                          1 if skip_single else 0, _stream()),
+                                          1 if skip_single else 0, _ptr(_status_word(q.device)), _stream()),
            f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
 
 
@@ -260,10 +272,7 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
         out = torch.empty(shape, dtype=torch.float32 if code == 1 else torch.bfloat16, device=a.device)
     assert out.shape == shape and out.stride(-1) == 1 and out.dtype == (torch.float32 if code == 1 else torch.bfloat16)
     assert k_splits == 1 or (code == 1 and out.is_contiguous())
-    status = _tc_status.get(a.device)
-    if status is None:
-        status = torch.zeros(1, dtype=torch.int32, device=a.device)
-        _tc_status[a.device] = status
+    status = _status_word(a.device)
     lib = load_family("gemm_bf16_tc")
     _check(lib.wllm_gemm_bf16_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
                                  k_splits, _ptr(status), max_ctas, _stream()),
