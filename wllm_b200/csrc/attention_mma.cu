@@ -5,8 +5,10 @@
 //
 //   decode   one CTA per (request with one new token, kv head, split of its keys).  The
 //            query heads of the kv head's group are the rows of one 16-row tile, so the
-//            keys are read once for the whole group.  The four warps take different
-//            16-key slices of every 64-key tile and merge at the end.  Splits of
+//            keys are read once for the whole group.  Head sizes in steps of 64 run the
+//            warp-specialised kernel (a TMA producer warp, three consumer warps that take
+//            whole 32-key tiles in turn); other head sizes run four warps that take 16-key
+//            slices of every 64-key tile.  The warps merge at the end.  Splits of
 //            `split_keys` keys give a long context to many SMs; each writes its partial
 //            (max, sum, unnormalised output) to scratch and a second kernel merges them
 //            in split order.  A request with a single split writes its output directly.
@@ -175,7 +177,7 @@ struct RowState {
 // One warp: its 16 query rows (at q_rows in shared memory) against NKEYS keys of a tile
 // that start at shared-memory row `key0`; `pos_r[i]`/`first_r[i]` bound the keys each of the
 // thread's two rows may see; `key_base` is the absolute index of tile row 0.
-template <int NKEYS, int QROWS>
+template <int NKEYS, int QROWS, int KROWS = BN>
 __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_row0, uint32_t k_tile, uint32_t v_tile, int key0,
                                           int key_base, const int (&pos_r)[2], const int (&first_r)[2], float scale2) {
     constexpr int NT = NKEYS / 8;
@@ -192,7 +194,7 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_r
 #pragma unroll
         for (int np = 0; np < NT / 2; ++np) {
             uint32_t b[4];
-            ldsm4(k_tile + swz<BN>(key0 + np * 16 + b_row, kt * 2 + b_chunk), b);
+            ldsm4(k_tile + swz<KROWS>(key0 + np * 16 + b_row, kt * 2 + b_chunk), b);
             mma16816(s[2 * np], a, b[0], b[1]);
             mma16816(s[2 * np + 1], a, b[2], b[3]);
         }
@@ -244,7 +246,7 @@ __device__ __forceinline__ void warp_tile(RowState& st, uint32_t q_tile, int q_r
 #pragma unroll
         for (int np = 0; np < NTO / 2; ++np) {
             uint32_t b[4];
-            ldsm4t(v_tile + swz<BN>(key0 + kk * 16 + v_row, np * 2 + v_chunk), b);
+            ldsm4t(v_tile + swz<KROWS>(key0 + kk * 16 + v_row, np * 2 + v_chunk), b);
             mma16816(st.o[2 * np], p, b[0], b[1]);
             mma16816(st.o[2 * np + 1], p, b[2], b[3]);
         }
@@ -417,6 +419,158 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
         float L = 0.f, O = 0.f;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) {
+            const float f = exp2f(sm_ml[(w * 16 + row) * 2] - mbase);
+            L += sm_ml[(w * 16 + row) * 2 + 1] * f;
+            O += sm_o[(size_t)(w * 16 + row) * HD + d] * f;
+        }
+        const int head = g * rep + row;
+        if (num_splits == 1) {
+            out[(size_t)token * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
+        } else {
+            const size_t slot = ((size_t)r * nq + head) * max_splits + split;
+            part_o[slot * HD + d] = O;
+            if (d == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------------------
+// decode, warp-specialised (head sizes in steps of 64): grid (max_splits, nkv, requests)
+// --------------------------------------------------------------------------------------
+// One producer warp and three consumer warps.  The producer's elected lane walks the split's keys in
+// tiles of 32 and fills a ring of six stages with TMA box copies (keys and values of one tile per stage);
+// tile n goes to consumer warp n % 3, which waits for it on the stage's "full" mbarrier, runs all 16
+// query rows against its 32 keys, and hands the stage back through the "empty" mbarrier.  No barrier
+// spans the CTA until the running states are merged at the end, so a warp that waits for memory or for
+// a dependent instruction stalls nobody else, and several tiles are in flight behind those in use.
+// The number of stages is a multiple of the number of consumers, so a stage is always served by the
+// same warp: a parity wait tells only the current phase from the one before it, and a warp that saw
+// every second fill of a stage could take an old phase for the one it is waiting for.
+constexpr int WS_BN = 32;
+constexpr int WS_STAGES = 6;
+constexpr int WS_CONSUMERS = 6;
+static_assert(WS_STAGES % WS_CONSUMERS == 0, "every stage must belong to one consumer warp");
+constexpr int WS_TILE_BYTES = WS_BN * ROWB;
+constexpr int WS_THREADS = (1 + WS_CONSUMERS) * 32;
+constexpr int WS_SMEM = 1024 + WS_STAGES * 2 * WS_TILE_BYTES + 16 * ROWB + 128;
+
+__global__ void __launch_bounds__(WS_THREADS)
+decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                 const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                 const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
+                 const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
+                 int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+                 int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+    if (req_q_len[r] != 1) return;
+    const int ctx = req_ctx_len[r], pos = ctx - 1;
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int num_splits = (ctx + split_keys - 1) / split_keys;
+    if (split >= num_splits) return;
+    const int key_lo = max(split * split_keys, first), key_hi = min(ctx, (split + 1) * split_keys);
+    const int rep = nq / nkv, token = req_q_start[r];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t q_s = base + WS_STAGES * 2 * WS_TILE_BYTES;
+    const uint32_t full0 = q_s + 16 * ROWB, empty0 = full0 + 8 * WS_STAGES;
+    const int* table = block_table + (size_t)r * max_pages;
+    const int page_shift = 31 - __clz(page_size);
+    const int t0 = key_lo / WS_BN, t1 = key_lo >= key_hi ? t0 : (key_hi + WS_BN - 1) / WS_BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < WS_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    load_q_tile<WS_THREADS, 16>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
+    cp_commit();
+    cp_wait<0>();
+    __syncthreads();
+
+    RowState st;
+    init_state(st);
+    bool ok = true;
+    if (warp == WS_CONSUMERS) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            const int box_rows = page_size < WS_BN ? page_size : WS_BN;
+            int n = 0;
+            for (int t = t0; t < t1; ++t, ++n) {
+                const int s = n % WS_STAGES;
+                if (!mbar_wait(empty0 + 8 * s, ((n / WS_STAGES) & 1) ^ 1)) { ok = false; break; }
+                const uint32_t k_dst = base + (2 * s) * WS_TILE_BYTES, v_dst = k_dst + WS_TILE_BYTES, bar = full0 + 8 * s;
+                mbar_expect_tx(bar, 2 * WS_TILE_BYTES);
+                for (int r0 = 0; r0 < WS_BN; r0 += box_rows) {
+                    const int key = t * WS_BN + r0, index = key >> page_shift;
+                    int page = index < max_pages ? table[index] : 0;
+                    if (page < 0) page = 0;
+                    const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+#pragma unroll
+                    for (int cb = 0; cb < HD / 64; ++cb) {
+                        tma_load_2d(k_dst + cb * (WS_BN * 128) + r0 * 128, &k_map, bar, cb * 64, row);
+                        tma_load_2d(v_dst + cb * (WS_BN * 128) + r0 * 128, &v_map, bar, cb * 64, row);
+                    }
+                }
+            }
+            // stay until the consumers have handed back every stage that was filled (a stage that was
+            // never filled passes at once), so that nothing is in flight when the CTA leaves
+            for (int k = 0; k < WS_STAGES && ok; ++k, ++n) {
+                const int s = n % WS_STAGES;
+                if (!mbar_wait(empty0 + 8 * s, ((n / WS_STAGES) & 1) ^ 1)) ok = false;
+            }
+            if (!ok) atomicExch(status, GAVE_UP_DECODE);
+        }
+    } else {
+        // ---------------- consumers: warp w takes tiles w, w + 3, ... ----------------
+        const int first_r[2] = {key_lo, key_lo};
+        const int hi_r[2] = {min(pos, key_hi - 1), min(pos, key_hi - 1)};
+        for (int n = warp; t0 + n < t1; n += WS_CONSUMERS) {
+            const int s = n % WS_STAGES;
+            if (!mbar_wait(full0 + 8 * s, (n / WS_STAGES) & 1)) { ok = false; break; }
+            __syncwarp();
+            const uint32_t k_src = base + (2 * s) * WS_TILE_BYTES;
+            warp_tile<WS_BN, 16, WS_BN>(st, q_s, 0, k_src, k_src + WS_TILE_BYTES, 0, (t0 + n) * WS_BN, hi_r, first_r, scale2);
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
+        }
+        if (!ok && lane == 0) atomicExch(status, GAVE_UP_DECODE);
+    }
+    __syncthreads();
+
+    // merge the consumer warps through shared memory (the ring is free now)
+    float* sm_o = reinterpret_cast<float*>(smem);                  // [warp][16][HD]
+    float* sm_ml = sm_o + WS_CONSUMERS * 16 * HD;                   // [warp][16][2]
+    if (warp < WS_CONSUMERS) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 1);
+            st.l[i] += __shfl_xor_sync(0xffffffffu, st.l[i], 2);
+        }
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NTO; ++n) {
+            float* o0 = sm_o + ((size_t)(warp * 16 + r0) * HD) + n * 8 + c0;
+            float* o1 = sm_o + ((size_t)(warp * 16 + r0 + 8) * HD) + n * 8 + c0;
+            o0[0] = st.o[n][0]; o0[1] = st.o[n][1];
+            o1[0] = st.o[n][2]; o1[1] = st.o[n][3];
+        }
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * 16 + r0) * 2] = st.m[0];      sm_ml[(warp * 16 + r0) * 2 + 1] = st.l[0];
+            sm_ml[(warp * 16 + r0 + 8) * 2] = st.m[1];  sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = st.l[1];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rep * HD; idx += WS_THREADS) {
+        const int row = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WS_CONSUMERS; ++w) M = fmaxf(M, sm_ml[(w * 16 + row) * 2]);
+        const float mbase = M == -INFINITY ? 0.f : M;
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < WS_CONSUMERS; ++w) {
             const float f = exp2f(sm_ml[(w * 16 + row) * 2] - mbase);
             L += sm_ml[(w * 16 + row) * 2 + 1] * f;
             O += sm_o[(size_t)(w * 16 + row) * HD + d] * f;
@@ -639,26 +793,35 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     if (requests <= 0) return WLLM_OK;
     const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
-    if (nq / nkv > 16 || split_keys < BN || split_keys % BN != 0 || max_splits < 1 || max_splits > MERGE_MAX_SPLITS)
+    const int tile = USE_TMA ? WS_BN : BN;      // splits are whole tiles of the kernel that runs
+    if (nq / nkv > 16 || split_keys < BN || split_keys % tile != 0 || max_splits < 1 || max_splits > MERGE_MAX_SPLITS)
         return WLLM_BAD_SIZE;
     CUtensorMap km, vm;
     const long long rows = pool_pages * nkv * page_size;
-    int r = pool_map(k_pages, rows, page_size < BN ? page_size : BN, &km);
+    const int box_rows = USE_TMA ? (page_size < WS_BN ? page_size : WS_BN) : (page_size < BN ? page_size : BN);
+    int r = pool_map(k_pages, rows, box_rows, &km);
     if (r) return r;
-    r = pool_map(v_pages, rows, page_size < BN ? page_size : BN, &vm);
+    r = pool_map(v_pages, rows, box_rows, &vm);
     if (r) return r;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        cudaError_t e = USE_TMA
+            ? cudaFuncSetAttribute(decode_ws_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM)
+            : cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)requests * nq * max_splits * HD;
-    decode_kernel<<<dim3(max_splits, nkv, requests), NTHREADS, DEC_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm, req_q_start,
-        req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys,
-        max_splits, part_o, part_ml, status);
+    if (USE_TMA)
+        decode_ws_kernel<<<dim3(max_splits, nkv, requests), WS_THREADS, WS_SMEM, stream>>>(
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len, block_table,
+            max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o, part_ml, status);
+    else
+        decode_kernel<<<dim3(max_splits, nkv, requests), NTHREADS, DEC_SMEM, stream>>>(
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
+            req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
+            split_keys, max_splits, part_o, part_ml, status);
     int st = wllm_launch_status();
     if (st || max_splits == 1) return st;
     merge_kernel<<<dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream>>>(

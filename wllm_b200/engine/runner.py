@@ -71,9 +71,10 @@ class StepContext:
         if decode:
             R = self.n_requests
             # one CTA fits on an SM: split every (request, kv head) so that all CTAs run in one wave,
-            # in whole 64-key tiles and not below 128 keys
+            # in whole tiles (32 keys in the warp-specialised kernel, else 64) and not below 128 keys
             per_head = max(1, SM_COUNT // (R * nkv))
-            split_keys = max(128, -(-(-(-self.max_ctx // per_head)) // 64) * 64)
+            tile = 32 if hd % 64 == 0 else 64
+            split_keys = max(128, -(-(-(-self.max_ctx // per_head)) // tile) * tile)
             max_splits = max(1, -(-self.max_ctx // split_keys))
             scratch = self.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
                                   torch.float32)
