@@ -12,6 +12,7 @@ __device__ __forceinline__ float act_silu(float x) { return x / (1.0f + expf(-x)
 
 template <typename T, int ACT>
 __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total) {
+    pdl_begin();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t n = idx / I, c = idx % I;
         const float g = to_f32(in[n * 2 * I + c]), u = to_f32(in[n * 2 * I + I + c]);
@@ -22,6 +23,7 @@ __global__ void gated_act_kernel(const T* __restrict__ in, T* __restrict__ out, 
 // bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, grid (column blocks, rows)
 template <int ACT>
 __global__ void gated_act_bf16x8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int I) {
+    pdl_begin();
     const int n = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= I) return;
@@ -46,17 +48,15 @@ WLLM_API int wllm_gated_act(const void* in, void* out, int dtype, int act, int n
     if (act != 0 && act != 1) return WLLM_BAD_SIZE;
     if (dtype == WLLM_BF16 && I % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         const dim3 grid((I / 8 + 127) / 128, n);
-        if (act == 0) gated_act_bf16x8_kernel<0><<<grid, 128, 0, stream>>>((const bf16*)in, (bf16*)out, I);
-        else gated_act_bf16x8_kernel<1><<<grid, 128, 0, stream>>>((const bf16*)in, (bf16*)out, I);
-        return wllm_launch_status();
+        if (act == 0) return wllm_launch(gated_act_bf16x8_kernel<0>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
+        return wllm_launch(gated_act_bf16x8_kernel<1>, grid, 128, 0, stream, (const bf16*)in, (bf16*)out, I);
     }
     const size_t total = (size_t)n * I;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-#define LAUNCH(T, A) gated_act_kernel<T, A><<<blocks, threads, 0, stream>>>((const T*)in, (T*)out, I, total)
-    if (dtype == WLLM_BF16) { if (act == 0) LAUNCH(bf16, 0); else LAUNCH(bf16, 1); }
-    else if (dtype == WLLM_F32) { if (act == 0) LAUNCH(float, 0); else LAUNCH(float, 1); }
-    else return WLLM_BAD_DTYPE;
+#define LAUNCH(T, A) wllm_launch(gated_act_kernel<T, A>, blocks, threads, 0, stream, (const T*)in, (T*)out, I, total)
+    if (dtype == WLLM_BF16) return act == 0 ? LAUNCH(bf16, 0) : LAUNCH(bf16, 1);
+    if (dtype == WLLM_F32) return act == 0 ? LAUNCH(float, 0) : LAUNCH(float, 1);
 #undef LAUNCH
-    return wllm_launch_status();
+    return WLLM_BAD_DTYPE;
 }

@@ -345,6 +345,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
               const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
               int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
+    pdl_begin();
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
@@ -462,6 +463,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
                  int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
                  int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
+    pdl_begin();
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
@@ -595,6 +597,7 @@ __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* 
                              const float* __restrict__ part_ml) {
     __shared__ float w[MERGE_MAX_SPLITS];
     __shared__ float inv_l;
+    pdl_begin();
     const int head = blockIdx.x, r = blockIdx.y;
     if (req_q_len[r] != 1) return;
     const int num_splits = (req_ctx_len[r] + split_keys - 1) / split_keys;
@@ -640,6 +643,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                int skip_single, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
+    pdl_begin();
     const int g = blockIdx.y, r = blockIdx.z;
     const int q_len = req_q_len[r];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
@@ -813,20 +817,21 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     }
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)requests * nq * max_splits * HD;
+    int st;
     if (USE_TMA)
-        decode_ws_kernel<<<dim3(max_splits, nkv, requests), WS_THREADS, WS_SMEM, stream>>>(
-            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len, block_table,
-            max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o, part_ml, status);
+        st = wllm_launch(decode_ws_kernel, dim3(max_splits, nkv, requests), WS_THREADS, WS_SMEM, stream,
+                         (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
+                         block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o,
+                         part_ml, status);
     else
-        decode_kernel<<<dim3(max_splits, nkv, requests), NTHREADS, DEC_SMEM, stream>>>(
-            (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
-            req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
-            split_keys, max_splits, part_o, part_ml, status);
-    int st = wllm_launch_status();
+        st = wllm_launch(decode_kernel, dim3(max_splits, nkv, requests), NTHREADS, DEC_SMEM, stream,
+                         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
+                         req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window,
+                         scale * LOG2E, split_keys, max_splits, part_o, part_ml, status);
     if (st || max_splits == 1) return st;
-    merge_kernel<<<dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream>>>(
-        (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits, part_o, part_ml);
-    return wllm_launch_status();
+    return wllm_launch(merge_kernel, dim3(nq, requests), HD >= 256 ? 256 : (HD >= 128 ? 128 : 64), 0, stream,
+                       (bf16*)out, out_stride, req_q_start, req_q_len, req_ctx_len, nq, split_keys, max_splits,
+                       (const float*)part_o, (const float*)part_ml);
 }
 
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
@@ -851,8 +856,8 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
         configured = true;
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
-    prefill_kernel<<<dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream>>>(
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm, req_q_start,
-        req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
-    return wllm_launch_status();
+    return wllm_launch(prefill_kernel, dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream,
+                       (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
+                       req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
+                       skip_single, status);
 }

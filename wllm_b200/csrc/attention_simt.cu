@@ -47,6 +47,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const int* __restrict__ block_table, int max_pages, int n_tokens, int nq, int nkv, int hd,
                             int page_size, int window, float scale) {
     extern __shared__ float q_smem[];
+    pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int item = blockIdx.x * WARPS + warp;
     if (item >= n_tokens * nq) return;
@@ -118,15 +119,14 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
                   int nq, int nkv, int hd, int page_size, int window, float scale, cudaStream_t stream) {
     const int blocks = (n_tokens * nq + WARPS - 1) / WARPS;
     const size_t smem = (size_t)WARPS * hd * sizeof(float);
-#define GO(NE) paged_attention_simt_kernel<T, NE><<<blocks, WARPS * 32, smem, stream>>>( \
+#define GO(NE) wllm_launch(paged_attention_simt_kernel<T, NE>, blocks, WARPS * 32, smem, stream, \
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, token_req, positions, \
         block_table, max_pages, n_tokens, nq, nkv, hd, page_size, window, scale)
-    if (hd <= 64) GO(2);
-    else if (hd <= 128) GO(4);
-    else if (hd <= 256) GO(8);
-    else GO(16);
+    if (hd <= 64) return GO(2);
+    if (hd <= 128) return GO(4);
+    if (hd <= 256) return GO(8);
+    return GO(16);
 #undef GO
-    return wllm_launch_status();
 }
 
 WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

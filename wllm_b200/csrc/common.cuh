@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define WLLM_API extern "C" __attribute__((visibility("default")))
 
@@ -27,6 +28,42 @@ template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __f
 
 static inline int wllm_launch_status() {
     cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? WLLM_OK : 1000 + (int)e;
+}
+
+// Programmatic dependent launch.  Every kernel of the engine begins with pdl_begin(): it lets the kernel
+// behind it in the stream be scheduled at once (launch_dependents), then waits until the kernel before it
+// has completed and its writes are visible (wait).  What a kernel does before its wait may touch shared
+// memory and read-only inputs that no kernel of the step writes (weights), nothing else.  Launched with
+// the attribute below, the launch latency and prologue of a kernel overlap the tail of its predecessor;
+// without it (WLLM_PDL=0) both instructions do nothing and the stream serialises as usual.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_begin() { pdl_launch_dependents(); pdl_wait(); }
+
+static inline bool wllm_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("WLLM_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int wllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = wllm_pdl_enabled() ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
     return e == cudaSuccess ? WLLM_OK : 1000 + (int)e;
 }
 

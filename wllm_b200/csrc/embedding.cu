@@ -5,6 +5,7 @@
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table, float scale,
                                     float* __restrict__ out, int H, int V) {
+    pdl_begin();
     const int row = blockIdx.x;
     int id = ids[row];
     float* o = out + (size_t)row * H;
@@ -22,10 +23,8 @@ WLLM_API int wllm_embed_gather(const int* ids, const void* table, int table_dtyp
     if (H <= 0 || V <= 0) return WLLM_BAD_SIZE;
     const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
     if (table_dtype == WLLM_BF16)
-        embed_gather_kernel<bf16><<<n, threads, 0, stream>>>(ids, (const bf16*)table, scale, out, H, V);
-    else if (table_dtype == WLLM_F32)
-        embed_gather_kernel<float><<<n, threads, 0, stream>>>(ids, (const float*)table, scale, out, H, V);
-    else
-        return WLLM_BAD_DTYPE;
-    return wllm_launch_status();
+        return wllm_launch(embed_gather_kernel<bf16>, n, threads, 0, stream, ids, (const bf16*)table, scale, out, H, V);
+    if (table_dtype == WLLM_F32)
+        return wllm_launch(embed_gather_kernel<float>, n, threads, 0, stream, ids, (const float*)table, scale, out, H, V);
+    return WLLM_BAD_DTYPE;
 }

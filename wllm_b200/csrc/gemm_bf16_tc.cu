@@ -129,6 +129,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_slot = tempty0 + 16;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_addr(smem_raw)));
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
     const int n_cols = GATED ? N / 2 : N;                       // columns of the output
@@ -157,17 +158,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // The weights are written by no kernel of the step: the first stages' W tiles are requested before
+            // this kernel waits for its predecessor, so they stream while that kernel still runs.  A (the
+            // activations the predecessor wrote) follows after the wait.
+            int early = 0;
+            if (blockIdx.x < num_tiles) {
+                const int tile = blockIdx.x;
+                const int mn = tile % tiles_mn, split = tile / tiles_mn;
+                const int n0 = (mn / tiles_m) * tile_n;
+                const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
+                early = min(STAGES, kb_hi - kb_lo);
+                for (int i = 0; i < early; ++i) {
+                    const uint32_t b_dst = ring + i * STAGE_BYTES + A_BYTES, bar = full0 + 8 * i;
+                    mbar_expect_tx(bar, STAGE_BYTES);
+                    tma_load_2d(b_dst, &map_w, bar, (kb_lo + i) * BK, n0);
+                    tma_load_2d(b_dst + B_HALF_BYTES, &map_w, bar, (kb_lo + i) * BK, GATED ? up_row_offset + n0 : n0 + 128);
+                }
+            }
+            pdl_wait();
+            int issued = 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int mn = tile % tiles_mn, split = tile / tiles_mn;
                 const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * tile_n;
                 const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
-                for (int kb = kb_lo; kb < kb_hi; ++kb) {
-                    if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
+                for (int kb = kb_lo; kb < kb_hi; ++kb, ++issued) {
                     const uint32_t a_dst = ring + stage * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = full0 + 8 * stage;
-                    mbar_expect_tx(bar, STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
-                    tma_load_2d(b_dst, &map_w, bar, kb * BK, n0);
-                    tma_load_2d(b_dst + B_HALF_BYTES, &map_w, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + 128);
+                    if (issued < early) {
+                        tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);       // W of this stage is already on its way
+                    } else {
+                        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
+                        mbar_expect_tx(bar, STAGE_BYTES);
+                        tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
+                        tma_load_2d(b_dst, &map_w, bar, kb * BK, n0);
+                        tma_load_2d(b_dst + B_HALF_BYTES, &map_w, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + 128);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -208,6 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else {
         // ---------------- epilogue: warps 2..5, each its own quarter of the 128 lanes ----------------
+        pdl_wait();                  // C may still be read by the kernel before this one
         const int quarter = warp & 3;
         uint32_t it = 0;
         bool ok = true;
@@ -351,9 +376,8 @@ static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, in
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
-    gemm_tc_kernel<EPI, AROWS><<<ctas, NUM_THREADS, Ring<AROWS>::SMEM_BYTES, stream>>>(ma, mw, c, ldc, M, N, K, up_off,
-                                                                                      k_splits, status);
-    return wllm_launch_status();
+    return wllm_launch(gemm_tc_kernel<EPI, AROWS>, ctas, NUM_THREADS, Ring<AROWS>::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
+                       up_off, k_splits, status);
 }
 
 static int a_rows_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }

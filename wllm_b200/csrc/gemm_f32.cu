@@ -43,6 +43,7 @@ gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
                 int ldc, int M, int N, int K) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_begin();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int ty = tid >> 4, tx = tid & 15;
@@ -88,7 +89,6 @@ WLLM_API int wllm_gemm_f32(const float* A, int lda, const float* W, int ldw, flo
     if (K <= 0 || lda < K || ldw < K || ldc < N) return WLLM_BAD_SIZE;
     const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     const bool vec = (K % 4 == 0) && (lda % 4 == 0) && (ldw % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0);
-    if (vec) gemm_f32_kernel<true><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
-    else gemm_f32_kernel<false><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
-    return wllm_launch_status();
+    if (vec) return wllm_launch(gemm_f32_kernel<true>, grid, 256, 0, stream, A, lda, W, ldw, C, ldc, M, N, K);
+    return wllm_launch(gemm_f32_kernel<false>, grid, 256, 0, stream, A, lda, W, ldw, C, ldc, M, N, K);
 }

@@ -68,6 +68,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
                                size_t delta_split_stride, const TW* __restrict__ w, float eps, float offset,
                                TO* __restrict__ out, const int* __restrict__ rows, int H) {
     __shared__ float scratch[32];
+    pdl_begin();
     const int i = blockIdx.x;
     const int row = rows ? rows[i] : i;
     float* r = resid + (size_t)row * H;
@@ -137,12 +138,12 @@ static int launch_out(float* resid, const void* delta, int delta_splits, size_t 
                      ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0 && delta_split_stride % 4 == 0;
     const int per = vec ? 4 : 1;
     const int threads = H / per >= 1024 ? 512 : (H / per >= 256 ? 256 : 128);
-#define GO(TO, V) rmsnorm_kernel<TD, TW, TO, V><<<n, threads, 0, stream>>>(resid, (const TD*)delta, delta_splits, delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H)
-    if (out_dtype == WLLM_BF16) { if (vec) GO(bf16, 4); else GO(bf16, 1); }
-    else if (out_dtype == WLLM_F32) { if (vec) GO(float, 4); else GO(float, 1); }
-    else return WLLM_BAD_DTYPE;
+#define GO(TO, V) wllm_launch(rmsnorm_kernel<TD, TW, TO, V>, n, threads, 0, stream, resid, (const TD*)delta, delta_splits, \
+                       delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H)
+    if (out_dtype == WLLM_BF16) return vec ? GO(bf16, 4) : GO(bf16, 1);
+    if (out_dtype == WLLM_F32) return vec ? GO(float, 4) : GO(float, 1);
 #undef GO
-    return wllm_launch_status();
+    return WLLM_BAD_DTYPE;
 }
 
 WLLM_API int wllm_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits, long long delta_split_stride,

@@ -20,6 +20,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
                                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
                                      TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
                                      int rot_dim, int page_size) {
+    pdl_begin();
     const int t = blockIdx.x, h = blockIdx.y;
     const TI* x = qkv + (size_t)t * row_stride + (size_t)h * hd;
     const int slot = slots ? slots[t] : -1;
@@ -70,13 +71,12 @@ WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, i
         return WLLM_BAD_SIZE;
     const int threads = hd >= 256 ? 128 : (hd >= 128 ? 64 : 32);
     const dim3 grid(n, nq + 2 * nkv);
-#define GO(TI, TO) rope_kv_write_kernel<TI, TO><<<grid, threads, 0, stream>>>((const TI*)qkv, row_stride, in_splits, \
+#define GO(TI, TO) wllm_launch(rope_kv_write_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)qkv, row_stride, in_splits, \
         (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
         rot_dim, page_size)
-    if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) GO(bf16, bf16);
-    else if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) GO(float, bf16);
-    else if (in_dtype == WLLM_F32 && out_dtype == WLLM_F32) GO(float, float);
-    else return WLLM_BAD_DTYPE;
+    if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) return GO(bf16, bf16);
+    if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) return GO(float, bf16);
+    if (in_dtype == WLLM_F32 && out_dtype == WLLM_F32) return GO(float, float);
 #undef GO
-    return wllm_launch_status();
+    return WLLM_BAD_DTYPE;
 }

@@ -61,6 +61,7 @@ sample_kernel(float* __restrict__ logits, int row_stride, int V, const float* __
     __shared__ int ibest[32];
     __shared__ float chunk_sums[THREADS];
     __shared__ int chosen;
+    pdl_begin();
     const int row = blockIdx.x, tid = threadIdx.x;
     float* x = logits + (size_t)row * row_stride;
 
@@ -211,7 +212,6 @@ WLLM_API int wllm_sample(float* logits, int row_stride, int rows, int V, const f
                          int* out_token, float* out_logprob, cudaStream_t stream) {
     if (rows <= 0) return WLLM_OK;
     if (V <= 0 || row_stride < V) return WLLM_BAD_SIZE;
-    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_k, top_p, min_p, penalty,
-                                                 seed_lo, seed_hi, counter, gen_offsets, gen_ids, out_token, out_logprob);
-    return wllm_launch_status();
+    return wllm_launch(sample_kernel, rows, THREADS, 0, stream, logits, row_stride, V, temperature, top_k, top_p, min_p, penalty,
+                       seed_lo, seed_hi, counter, gen_offsets, gen_ids, out_token, out_logprob);
 }

@@ -131,6 +131,13 @@ def compile_family(family: str, defines: dict | None = None, verbose: bool = Tru
                     os.unlink(tmp)
                 raise KernelBuildError(f"nvcc failed on {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")
             os.replace(tmp, out)
+            prefix = name.rsplit("-", 1)[0] + "-"
+            for old in os.listdir(out_dir):      # objects of earlier versions of this family and variant
+                if old.startswith(prefix) and old.endswith(".so") and old != name:
+                    try:
+                        os.unlink(os.path.join(out_dir, old))
+                    except OSError:
+                        pass
             if verbose:
                 print(f"[wllm_b200]   {family} done in {time.time() - start:.1f} s", file=sys.stderr, flush=True)
         finally:
