@@ -1,0 +1,84 @@
+"""The engine at the real layer widths of Gemma-2B and Gemma-7B (two layers each, the whole
+256,000-token vocabulary, random weights): logits under several ways of cutting against the
+plain implementation run in float32 on the host, in 32-bit (also bit-equal across cuts) and
+in bfloat16.  These are the sizes at which index arithmetic, tile tails and split plans of
+the kernels differ from the tiny configurations."""
+import os
+
+import pytest
+import torch
+from safetensors.torch import load_file
+
+import plain_gemma as plain
+import traces
+from helpers import max_diff
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = {
+    "2b": dict(hidden_size=2048, num_attention_heads=8, num_key_value_heads=1, head_dim=256, intermediate_size=16384),
+    "7b": dict(hidden_size=3072, num_attention_heads=16, num_key_value_heads=16, head_dim=256, intermediate_size=24576),
+}
+
+
+def config(name):
+    return dict(architectures=["GemmaForCausalLM"], model_type="gemma", num_hidden_layers=2, vocab_size=256000,
+                max_position_embeddings=8192, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                **SHAPES[name])
+
+
+@pytest.fixture(scope="module", params=["2b", "7b"])
+def model(request, tmp_path_factory):
+    from wllm_b200.weights import write_random_model
+    name = request.param
+    cfg = config(name)
+    folder = write_random_model(str(tmp_path_factory.mktemp(name) / "m"), cfg, seed=3)
+    w = {k: v.float() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    g = torch.Generator().manual_seed(2)
+    reqs = {"a": torch.randint(0, cfg["vocab_size"], (150,), generator=g).tolist(),
+            "b": torch.randint(0, cfg["vocab_size"], (70,), generator=g).tolist(),
+            "c": torch.randint(0, cfg["vocab_size"], (3,), generator=g).tolist()}
+    # the plain implementation's logits at a handful of places per request (the head is 256,000 wide)
+    wanted = {"a": [0, 1, 63, 64, 100, 149], "b": [0, 15, 16, 69], "c": [0, 2]}
+    ref = {}
+    for rid, toks in reqs.items():
+        logits = plain.forward(toks, w, cfg)
+        for p in wanted[rid]:
+            ref[(rid, p)] = logits[p].clone()
+    return name, folder, reqs, ref
+
+
+def run(folder, dtype, steps, keys):
+    from test_gpu_replay import gpu_runner
+    pages = -(-traces.peak_tokens(steps) // 16)
+    rows = traces.run_in_process(gpu_runner(folder, dtype, 16, pages), steps)
+    return {k: rows[k] for k in keys}
+
+
+def cuts(reqs):
+    return {"whole": traces.whole(reqs), "tail": traces.tail_singly(reqs, tail=8),
+            "portions": traces.portions(reqs, sizes=(64, 7, 2, 33, 70, 1)), "mixed": traces.mixed(reqs, seed=4, decode_tail=5)}
+
+
+def test_32bit_matches_plain_and_is_bit_equal_across_cuts(model):
+    name, folder, reqs, ref = model
+    first = None
+    for cut, steps in cuts(reqs).items():
+        rows = run(folder, torch.float32, steps, ref.keys())
+        assert max_diff(rows, ref) < 2e-4, (name, cut)       # logits of order 1 over sums of 16k-24k terms
+        if first is None:
+            first = rows
+        else:
+            bad = sorted(k for k in first if not torch.equal(first[k], rows[k]))
+            assert not bad, f"{name} {cut}: first differing (request, position) {bad[0]}"
+
+
+def test_bfloat16_matches_plain_under_every_cut(model):
+    name, folder, reqs, ref = model
+    scale = max(float(r.abs().max()) for r in ref.values())
+    for cut, steps in cuts(reqs).items():
+        rows = run(folder, torch.bfloat16, steps, ref.keys())
+        assert max_diff(rows, ref) < 0.03 * max(1.0, scale), (name, cut)
+        for k in ref:     # and the ranking of the top token survives, or is a near-tie
+            top = int(ref[k].argmax())
+            assert float(ref[k][top] - ref[k][int(rows[k].argmax())]) < 0.03 * max(1.0, scale), (name, cut, k)
