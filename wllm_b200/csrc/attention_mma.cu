@@ -13,8 +13,10 @@
 //            (max, sum, unnormalised output) to scratch and a second kernel merges them
 //            in split order.  A request with a single split writes its output directly.
 //   prefill  one CTA per (request with several new tokens, kv head, tile of 128 rows),
-//            rows = (token, query head of the group); the eight warps own 16 rows each and
-//            walk all 64-key tiles up to the causal edge.
+//            rows = (token, query head of the group).  Head sizes in steps of 64 run on
+//            tcgen05 (scores and output accumulate in tensor memory, see prefill_tc_kernel);
+//            other head sizes on mma.sync: eight warps own 16 rows each and walk all 64-key
+//            tiles up to the causal edge.
 //
 // Keys and values come straight from the pages through the request's block table
 // ([page][kv_head][slot][head_dim] layout) into a swizzled multi-stage ring in shared memory.
@@ -27,9 +29,8 @@
 // exponentials are exp2 of log2(e)-scaled scores.  Which requests each kernel serves is
 // read from q_len on the device (1: decode, more: prefill), so a captured graph stays
 // valid when the batch changes its contents but not its shape.
-#include "common.cuh"
+#include "tc_common.cuh"
 
-#include <cuda.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -50,7 +51,6 @@ constexpr int NTHREADS = NWARPS * 32;
 constexpr int TILE_BYTES = BN * ROWB;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr bool USE_TMA = (HD % 64 == 0);
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
 enum { GAVE_UP_DECODE = 21, GAVE_UP_PREFILL = 22 };
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile of ROWS rows.  cp.async layout: rows of
@@ -61,26 +61,7 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     if (USE_TMA) return (uint32_t)((chunk >> 3) * (ROWS * 128) + row * 128 + ((((chunk ^ row) & 7)) << 4));
     return (uint32_t)(row * ROWB + ((((chunk & ~7) | ((chunk ^ row) & 7))) << 4));
 }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return smem_addr(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
@@ -717,6 +698,279 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     }
 }
 
+#if (HEAD_DIM % 64 == 0)
+// --------------------------------------------------------------------------------------
+// prefill on the fifth-generation tensor cores (head sizes in steps of 64): grid as above
+// --------------------------------------------------------------------------------------
+// 128 query rows per CTA are the 128 lanes of tensor memory.  Roles by warp:
+//   warp 0      one lane issues the TMA box copies of the key tiles and the value tiles (64 keys each,
+//               two stages each, keys and values on barriers of their own: a key stage is free as soon as
+//               its scores are computed, a value stage once it has been accumulated);
+//   warp 1      one lane issues tcgen05.mma: scores S = Q K^T (M 128, N 64, K = head size) into one of two
+//               score buffers in tensor memory, one tile ahead of the softmax, and O += P V (M 128,
+//               N = head size, K 64) with P from shared memory and V as an MN-major operand straight
+//               from the value tile (no transpose);
+//   warps 2-5   one thread per row: read the row's 64 scores with tcgen05.ld, mask, scale, running maximum
+//               and sum in registers without a shuffle, write P as bfloat16 into shared memory in the
+//               layout the tensor core reads, and rescale the row of O in tensor memory only when some
+//               row of the warp has a new maximum.  At the end they normalise O and store it.
+// All waits are bounded; a role that gives up records a code and every role leaves through the common
+// exit, where tensor memory is freed.
+constexpr int TC_BM = 128, TC_BN = 64, TC_KV_STAGES = 2;
+constexpr int TC_Q_BYTES = TC_BM * ROWB, TC_KV_BYTES = TC_BN * ROWB, TC_P_BYTES = TC_BM * 128;
+constexpr int TC_SMEM = 1024 + TC_Q_BYTES + 2 * TC_KV_STAGES * TC_KV_BYTES + TC_P_BYTES + 256;
+constexpr int TC_THREADS = 192;
+constexpr int TC_S_COL = 256;                      // score buffers behind the output accumulator
+constexpr uint32_t IDESC_S = umma_idesc(TC_BM, TC_BN, false, false);
+constexpr uint32_t IDESC_PV = umma_idesc(TC_BM, HD, false, true);       // V is MN-major
+enum { GAVE_UP_TC_LOAD = 23, GAVE_UP_TC_MMA = 24, GAVE_UP_TC_SOFTMAX = 25 };
+
+__device__ __forceinline__ float fast_exp2(float x) {       // ex2.approx: 2 ulp, exp2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                  const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                  const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
+                  const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
+                  int skip_single, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    pdl_begin();
+    const int g = blockIdx.y, r = blockIdx.z;
+    const int q_len = req_q_len[r];
+    if (q_len <= 0 || (skip_single && q_len == 1)) return;
+    const int rep = nq / nkv, rows = q_len * rep;
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int row0 = tile * TC_BM;
+    if (row0 >= rows) return;
+    const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = base, k_s = q_s + TC_Q_BYTES, v_s = k_s + TC_KV_STAGES * TC_KV_BYTES;
+    const uint32_t p_s = v_s + TC_KV_STAGES * TC_KV_BYTES, bars = p_s + TC_P_BYTES;
+    const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56;
+    const uint32_t s_full = bars + 72, s_empty = bars + 88, p_full = bars + 104, pv_done = bars + 112, tmem_slot = bars + 120;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    const int last_row = min(rows, row0 + TC_BM) - 1;
+    const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + row0 / rep;
+    const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
+    const int t0 = key_lo / TC_BN, t1 = (key_hi + TC_BN - 1) / TC_BN, T = t1 - t0;
+    const int page_shift = 31 - __clz(page_size);
+    const int* table = block_table + (size_t)r * max_pages;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 4);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
+            mbar_init(s_full + 8 * s, 1); mbar_init(s_empty + 8 * s, 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tc_alloc(tmem_slot, 512);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const int box_rows = page_size < TC_BN ? page_size : TC_BN;
+            bool ok = true;
+            int n = 0;
+            for (; n < T && ok; ++n) {
+                const int s = n & 1, ph = (n >> 1) & 1, tile_start = (t0 + n) * TC_BN;
+                for (int kv = 0; kv < 2 && ok; ++kv) {
+                    if (!mbar_wait((kv ? v_empty : k_empty) + 8 * s, ph ^ 1)) { ok = false; break; }
+                    const uint32_t bar = (kv ? v_full : k_full) + 8 * s, dst = (kv ? v_s : k_s) + s * TC_KV_BYTES;
+                    mbar_expect_tx(bar, TC_KV_BYTES);
+                    for (int r0 = 0; r0 < TC_BN; r0 += box_rows) {
+                        const int key = tile_start + r0, index = key >> page_shift;
+                        int page = index < max_pages ? table[index] : 0;
+                        if (page < 0) page = 0;
+                        const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+#pragma unroll
+                        for (int cb = 0; cb < HD / 64; ++cb)
+                            tma_load_2d(dst + cb * (TC_BN * 128) + r0 * 128, kv ? &v_map : &k_map, bar, cb * 64, row);
+                    }
+                }
+            }
+            // stay until the stages that were filled have been handed back: nothing in flight at the exit
+            for (int k = 0; k < 2 && ok; ++k, ++n) {
+                const int s = n & 1, ph = (n >> 1) & 1;
+                if (!mbar_wait(k_empty + 8 * s, ph ^ 1) || !mbar_wait(v_empty + 8 * s, ph ^ 1)) ok = false;
+            }
+            if (!ok) atomicExch(status, GAVE_UP_TC_LOAD);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            bool ok = mbar_wait(q_full, 0);
+            auto issue_scores = [&](int n) -> bool {       // S(n) = Q K(n)^T into score buffer n % 2
+                const int s = n & 1, ph = (n >> 1) & 1;
+                if (!mbar_wait(k_full + 8 * s, ph) || !mbar_wait(s_empty + 8 * s, ph ^ 1)) return false;
+                tc_fence_after();
+                const uint32_t d = tmem_base + TC_S_COL + s * TC_BN, kb = k_s + s * TC_KV_BYTES;
+#pragma unroll
+                for (int kt = 0; kt < HD / 16; ++kt)
+                    tc_mma(d, smem_desc(q_s + (kt >> 2) * (TC_BM * 128) + (kt & 3) * 32),
+                           smem_desc(kb + (kt >> 2) * (TC_BN * 128) + (kt & 3) * 32), IDESC_S, kt > 0 ? 1u : 0u);
+                tc_commit(k_empty + 8 * s);
+                tc_commit(s_full + 8 * s);
+                return true;
+            };
+            ok = ok && issue_scores(0);
+            for (int n = 0; n < T && ok; ++n) {
+                if (n + 1 < T && !issue_scores(n + 1)) { ok = false; break; }
+                const int s = n & 1, ph = (n >> 1) & 1;
+                if (!mbar_wait(v_full + 8 * s, ph) || !mbar_wait(p_full, n & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t vb = v_s + s * TC_KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < TC_BN / 16; ++kk)
+                    tc_mma(tmem_base, smem_desc(p_s + kk * 32), smem_desc_mn(vb + kk * (16 * 128), TC_BN * 128), IDESC_PV,
+                           (n > 0 || kk > 0) ? 1u : 0u);
+                tc_commit(v_empty + 8 * s);
+                tc_commit(pv_done);
+            }
+            if (!ok) atomicExch(status, GAVE_UP_TC_MMA);
+        }
+    } else {
+        // ---------------- softmax: one thread per row ----------------
+        const int quarter = warp & 3, row = quarter * 32 + lane, m_row = row0 + row;
+        const int epi_tid = threadIdx.x - 64;
+        // the query tile, in the layout the tensor core reads (the same swizzle as a box copy)
+        for (int idx = epi_tid; idx < TC_BM * CPR; idx += 128) {
+            const int rr = idx / CPR, chunk = idx % CPR, m = row0 + rr;
+            const bool valid = m < rows;
+            const bf16* src = valid ? q + (size_t)(q_start + m / rep) * q_stride + (size_t)(g * rep + m % rep) * HD + chunk * 8 : q;
+            cp_async16(q_s + swz<TC_BM>(rr, chunk), src, valid);
+        }
+        cp_commit();
+        cp_wait<0>();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(q_full);
+
+        const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
+        const int first_row = window > 0 ? max(0, pos_row - window + 1) : 0;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int n = 0; n < T; ++n) {
+            const int b = n & 1, ph = (n >> 1) & 1, key0 = (t0 + n) * TC_BN;
+            if (!mbar_wait(s_full + 8 * b, ph)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sv[2][32];
+            tc_ld32(t_lane + TC_S_COL + b * TC_BN, sv[0]);
+            tc_ld32(t_lane + TC_S_COL + b * TC_BN + 32, sv[1]);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty + 8 * b);          // the score buffer may be overwritten
+            // Scores stay unscaled until the exponent: max(scale * s) = scale * max(s) for scale > 0, and
+            // exp2(scale * s - scale * m) is one fused multiply-add and one ex2 per element.  Only tiles at the
+            // causal edge or the window's start need the per-key mask; the warp decides together.
+            const bool inner = __all_sync(0xffffffffu, key0 + TC_BN - 1 <= pos_row && key0 >= first_row);
+            float mx = -INFINITY;
+            if (inner) {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 64; ++c) {
+                    const int key = key0 + c;
+                    const float v = (key <= pos_row && key >= first_row) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
+                    sv[c >> 5][c & 31] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            }
+            const float m_new = fmaxf(m_run, mx * scale2);
+            const float mbase = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = fast_exp2(m_run - mbase);
+            float sum = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int c = 0; c < 64; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, -mbase));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), scale2, -mbase));
+                sum += p0 + p1;
+                packed[c >> 1] = pack_bf16(p0, p1);
+            }
+            l_run = l_run * corr + sum;
+            const bool changed = m_new > m_run;
+            m_run = m_new;
+            if (n > 0) {
+                if (!mbar_wait(pv_done, (n - 1) & 1)) { ok = false; break; }     // P and O of the tile before are done with
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t ov[32];
+                        tc_ld32(t_lane + c0, ov);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * corr);
+                        tc_st32(t_lane + c0, ov);
+                    }
+                    tc_wait_st();
+                }
+            }
+            // P row: 64 bfloat16 = eight 16-byte chunks, swizzled like a box copy
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t addr = p_s + row * 128 + ((j ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * j]), "r"(packed[4 * j + 1]),
+                             "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3]) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok && !mbar_wait(pv_done, (T - 1) & 1)) ok = false;
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l_run;
+            bf16* dst = m_row < rows ? out + (size_t)(q_start + m_row / rep) * out_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t ov[32];
+                tc_ld32(t_lane + c0, ov);
+                tc_wait_ld();
+                if (dst) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv);
+                        o.y = pack_bf16(__uint_as_float(ov[c + 2]) * inv, __uint_as_float(ov[c + 3]) * inv);
+                        o.z = pack_bf16(__uint_as_float(ov[c + 4]) * inv, __uint_as_float(ov[c + 5]) * inv);
+                        o.w = pack_bf16(__uint_as_float(ov[c + 6]) * inv, __uint_as_float(ov[c + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = o;
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(status, GAVE_UP_TC_SOFTMAX);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tc_dealloc(tmem_base, 512);
+    }
+}
+#endif
+
 // --------------------------------------------------------------------------------------
 // host side: tensor maps over the pools (cached by pointer and shape), entry points
 // --------------------------------------------------------------------------------------
@@ -850,12 +1104,27 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
     r = pool_map(v_pages, rows, page_size < BN ? page_size : BN, &vm);
     if (r) return r;
     static bool configured = false;
+#if (HEAD_DIM % 64 == 0)
+    static bool use_tc = false;
+#endif
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM);
         if (e != cudaSuccess) return 1000 + (int)e;
+#if (HEAD_DIM % 64 == 0)
+        e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        const char* legacy = getenv("WLLM_ATTENTION_MMA");       // =1: the mma.sync kernel, for comparison
+        use_tc = !(legacy && legacy[0] == '1');
+#endif
         configured = true;
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
+#if (HEAD_DIM % 64 == 0)
+    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0))
+        return wllm_launch(prefill_tc_kernel, dim3(tiles, nkv, requests), TC_THREADS, TC_SMEM, stream,
+                           (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
+                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
+#endif
     return wllm_launch(prefill_kernel, dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream,
                        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                        req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
