@@ -80,3 +80,16 @@ def test_greedy_ties_take_the_lowest_id():
     logits[1, 299] = 1.0
     tokens, _ = run(logits, [SamplingParams()] * 2, [0, 0], [0, 0], [set(), set()])
     assert tokens == [17, 299]
+
+
+@pytest.mark.parametrize("V", [31, 1000, 256000])
+def test_all_greedy_batches_take_the_two_stage_path(V):
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(5, V, generator=g) * 4.0
+    logits[2, V - 1] = 50.0                      # the last token of the last chunk
+    logits[3, 0] = logits[3, V // 2] = 60.0      # equal maxima in different chunks: the lower id wins
+    tokens, logprobs = run(logits, [SamplingParams()] * 5, [0] * 5, [0] * 5, [set()] * 5)
+    want = torch.log_softmax(logits.double(), dim=-1)
+    assert tokens == logits.argmax(-1).tolist() and tokens[2] == V - 1 and tokens[3] == 0
+    for i, t in enumerate(tokens):
+        assert abs(logprobs[i] - float(want[i, t])) < 2e-4

@@ -56,6 +56,7 @@ class RequestCache:
     reserved: int = 0          # tokens reserved by the step in flight
     closed: bool = False
     released_upto: list = field(default_factory=list)   # per group: pages below this index were given back
+    version: int = 0           # bumped whenever a table changes (lets a reader cache a copy)
 
 
 class CacheGroup:
@@ -175,6 +176,7 @@ class CacheManager:
             for g, table in zip(self.groups, rc.tables):
                 while len(table) < target:
                     table.append(g.pool.take())
+                    rc.version += 1
             rc.reserved += n
         for gi, g in enumerate(self.groups):
             used = g.pool.num_pages - g.pool.num_free
@@ -201,6 +203,7 @@ class CacheManager:
             for i in range(rc.released_upto[gi], upto):
                 g.pool.give(rc.tables[gi][i])
                 rc.tables[gi][i] = -1
+                rc.version += 1
             rc.released_upto[gi] = max(rc.released_upto[gi], upto)
 
     def cancel_reservation(self, rc: RequestCache) -> None:
@@ -210,6 +213,7 @@ class CacheManager:
         for g, table in zip(self.groups, rc.tables):
             while len(table) > target:
                 g.pool.give(table.pop())
+                rc.version += 1
 
     # -- figures -------------------------------------------------------------------
     def free_pages(self) -> list:

@@ -206,6 +206,78 @@ sample_kernel(float* __restrict__ logits, int row_stride, int V, const float* __
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// greedy rows without a penalty: two short kernels instead of one block per row
+// ------------------------------------------------------------------------------------------------
+// Stage 1, grid (chunks, rows): arg-max (lowest id among equals), maximum and sum of exp(x - max) of one
+// chunk of a row.  Stage 2, one warp per row: the chunks' results combined in chunk order.  A row of
+// 256,000 logits is read once, by 32 blocks instead of one.
+constexpr int GREEDY_CHUNKS = 32;
+
+__global__ void __launch_bounds__(256)
+greedy_stats_kernel(const float* __restrict__ logits, int row_stride, int V, float* __restrict__ stats) {
+    __shared__ float fs[32];
+    __shared__ int is[32];
+    pdl_begin();
+    const int chunk = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+    const int per = (V + GREEDY_CHUNKS - 1) / GREEDY_CHUNKS;
+    const int lo = chunk * per, hi = min(V, lo + per);
+    const float* x = logits + (size_t)row * row_stride;
+    float best = -INFINITY;
+    int best_i = V;
+    for (int i = lo + tid; i < hi; i += 256) {
+        const float v = x[i];
+        if (v > best) { best = v; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if ((tid & 31) == 0) { fs[tid >> 5] = best; is[tid >> 5] = best_i; }
+    __syncthreads();
+    best = fs[0]; best_i = is[0];
+    for (int w = 1; w < 8; ++w)
+        if (fs[w] > best || (fs[w] == best && is[w] < best_i)) { best = fs[w]; best_i = is[w]; }
+    __syncthreads();
+    float z = 0.f;
+    for (int i = lo + tid; i < hi; i += 256) z += expf(x[i] - best);
+    z = block_sum(z, fs);
+    if (tid == 0) {
+        float* out = stats + ((size_t)row * GREEDY_CHUNKS + chunk) * 3;
+        out[0] = best; out[1] = __int_as_float(best_i); out[2] = z;
+    }
+}
+
+__global__ void greedy_pick_kernel(const float* __restrict__ stats, int* __restrict__ out_token, float* __restrict__ out_logprob) {
+    pdl_begin();
+    const int row = blockIdx.x, lane = threadIdx.x;      // 32 threads, one chunk each
+    const float* s = stats + ((size_t)row * GREEDY_CHUNKS + lane) * 3;
+    float best = s[0];
+    int best_i = __float_as_int(s[1]);
+    const float m = best, z = s[2];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    float total = z == 0.f ? 0.f : z * expf(m - best);     // an empty chunk has max -inf and sum 0
+    total = warp_sum(total);
+    if (lane == 0) { out_token[row] = best_i; out_logprob[row] = -logf(total); }
+}
+
+// Greedy tokens and their log-probabilities (temperature 1) for `rows` rows; `stats` holds rows * 96 floats.
+WLLM_API int wllm_sample_greedy(const float* logits, int row_stride, int rows, int V, float* stats, int* out_token,
+                                float* out_logprob, cudaStream_t stream) {
+    if (rows <= 0) return WLLM_OK;
+    if (V <= 0 || row_stride < V) return WLLM_BAD_SIZE;
+    const int st = wllm_launch(greedy_stats_kernel, dim3(GREEDY_CHUNKS, rows), 256, 0, stream, logits, row_stride, V, stats);
+    if (st) return st;
+    return wllm_launch(greedy_pick_kernel, rows, 32, 0, stream, (const float*)stats, out_token, out_logprob);
+}
+
 WLLM_API int wllm_sample(float* logits, int row_stride, int rows, int V, const float* temperature, const int* top_k,
                          const float* top_p, const float* min_p, const float* penalty, const int* seed_lo,
                          const int* seed_hi, const int* counter, const int* gen_offsets, const int* gen_ids,

@@ -96,6 +96,7 @@ class ModelRunner:
         self.steps = 0
         self.tokens_run = 0
         self.h2d_bytes = 0
+        self._tables: dict = {}        # cached int32 copies of block tables
         self._graphs_on = False
         self._graphs: dict = {}        # (requests, table width) -> captured decode step
         self.graph_launches = 0        # kernel launches replayed from graphs so far
@@ -136,7 +137,29 @@ class ModelRunner:
             return host[o:o + n]
         start = 0
         wants = []
-        for r, e in enumerate(entries):
+        if N == R:
+            # every request brings one token (a decode step): whole columns at once, tables from cached copies
+            bases = [e.cache.num_tokens for e in entries]
+            view("token_ids")[:] = [e.tokens[0] for e in entries]
+            view("positions")[:] = bases
+            ar = np.arange(R, dtype=np.int32)
+            view("token_req")[:] = ar
+            view("req_q_start")[:] = ar
+            view("req_q_len")[:] = 1
+            view("req_ctx_len")[:] = np.asarray(bases, dtype=np.int32) + 1
+            view("req_slot")[:] = [e.cache.slot for e in entries]
+            for g in range(G):
+                view(f"slots{g}")[:] = [e.cache.tables[g][b // ps] * ps + b % ps for e, b in zip(entries, bases)]
+                rows2d = view(f"table{g}").reshape(R, P)
+                for r, e in enumerate(entries):
+                    t = self._table_copy(e.cache, g)
+                    rows2d[r, :t.shape[0]] = t
+            for r, e in enumerate(entries):
+                wants.extend(r + w for w in e.want)
+            entries_loop = ()
+        else:
+            entries_loop = enumerate(entries)
+        for r, e in entries_loop:
             n, base = lens[r], e.cache.num_tokens
             view("token_ids")[start:start + n] = e.tokens
             view("positions")[start:start + n] = np.arange(base, base + n, dtype=np.int32)
@@ -177,6 +200,17 @@ class ModelRunner:
         ctx.group_slots = [dev(f"slots{g}") for g in range(G)]
         ctx.group_tables = [dev(f"table{g}").view(R, P) for g in range(G)]
         return ctx
+
+    def _table_copy(self, rc, group: int) -> np.ndarray:
+        """A request's block table of one group as an int32 array, rebuilt only when the table changed."""
+        key = (id(rc), group)
+        hit = self._tables.get(key)
+        if hit is None or hit[0] != rc.version or hit[2] is not rc:
+            if len(self._tables) > 4096:
+                self._tables.clear()
+            hit = (rc.version, np.asarray(rc.tables[group], dtype=np.int32), rc)
+            self._tables[key] = hit
+        return hit[1]
 
     def _validate(self, entries: list) -> None:
         vocab, limit = self.model.plan.vocab_size, self.model.plan.max_positions

@@ -23,6 +23,7 @@ class Sampler:
         self.device = torch.device(device)
         self._ring = PinnedRing(self.device)
         self._dev = self._out = self._out_host = None
+        self._stats = None               # per-chunk (max, arg-max, sum) of the greedy path
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -40,11 +41,30 @@ class Sampler:
         out = self._out_host[:2 * rows].numpy()
         return out[:rows].tolist(), out[rows:].view(np.float32).tolist()
 
+    def _launch_greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        """All rows greedy and unpenalised: no options to send; arg-max and log-sum-exp by 32 blocks a row."""
+        rows, V = logits.shape
+        if self._out is None or self._out.numel() < 2 * rows:
+            cap = max(2 * rows, 1024)
+            self._out = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self._out_host = torch.empty(cap, dtype=torch.int32).pin_memory()
+        if self._stats is None or self._stats.numel() < rows * 96:
+            self._stats = torch.empty(max(rows, 64) * 96, dtype=torch.float32, device=self.device)
+        lib = load_family("sampling")
+        ops._check(lib.wllm_sample_greedy(c_void_p(logits.data_ptr()), logits.stride(0), rows, V,
+                                          c_void_p(self._stats.data_ptr()), c_void_p(self._out.data_ptr()),
+                                          c_void_p(self._out.data_ptr() + 4 * rows), ops._stream()), "sample_greedy")
+        ops.launches += 1
+        self.h2d_bytes = 0
+        return self._out[:rows]
+
     def launch(self, logits: torch.Tensor, params: list, counters: list, seeds: list, generated: list):
         """Enqueue the sampling of all rows; tokens [rows] int32 stay on the device (returned view)."""
         rows, V = logits.shape
         if logits.dtype != torch.float32 or logits.stride(1) != 1:
             raise ops.KernelError("sampling needs float32 logits with unit stride along the vocabulary")
+        if all(p.temperature == 0.0 and p.repetition_penalty == 1.0 for p in params):
+            return self._launch_greedy(logits)
         gen_lists = [sorted(g) if p.repetition_penalty != 1.0 else [] for p, g in zip(params, generated)]
         offsets = np.zeros(rows + 1, dtype=np.int32)
         offsets[1:] = np.cumsum([len(g) for g in gen_lists])
