@@ -222,7 +222,7 @@ def reference_arm(args) -> int:
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "wllm")):
         return unavailable("the reference is not installed under baseline/_ref (pip install --no-index --no-deps "
-                           "--target baseline/_ref /root/reference)")
+                           "--target baseline/_ref <reference checkout>)")
     sys.path.insert(0, ref)
     try:
         import torch
