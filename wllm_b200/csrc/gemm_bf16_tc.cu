@@ -51,10 +51,75 @@ enum { GAVE_UP_PRODUCER = 11, GAVE_UP_MMA = 12, GAVE_UP_EPILOGUE = 13 };
 
 constexpr uint32_t IDESC = umma_idesc(BM, BN, false, false);      // both operands K-major
 
+// gelu_tanh(x) = x/2 (1 + tanh u) = x / (1 + e^(-2u)),  u = sqrt(2/pi) (x + 0.044715 x^3): one exponential
+// and one division instead of a tanh.
 __device__ __forceinline__ float epi_gelu(float x) {
-    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    return __fdividef(x, 1.0f + __expf(-2.0f * u));
 }
-__device__ __forceinline__ float epi_silu(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float epi_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+// Epilogue of one warp for one tile: reads its 32 lanes of the accumulator at t_acc (tile_n columns; for the
+// gated epilogues gate in columns 0-127 and up in 128-255), applies the epilogue and stores rows m0 + 32 *
+// quarter + lane of C.
+template <int EPI>
+__device__ __forceinline__ void drain_accumulator(void* __restrict__ c, int ldc, int M, int n_cols, int tile_n, int split, int m0,
+                                                  int n0, uint32_t t_acc, int quarter, int lane) {
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    const int row = m0 + quarter * 32 + lane;
+    const uint32_t t_row = t_acc + ((uint32_t)(quarter * 32) << 16);
+    const bool quarter_has_rows = m0 + quarter * 32 < M;     // the same for the whole warp
+#pragma unroll 1
+    for (int c0 = 0; c0 < tile_n && quarter_has_rows; c0 += 32) {
+        uint32_t v[32];
+        float f[32];
+        tc_ld32(t_row + c0, v);
+        if (GATED) {
+            uint32_t u[32];
+            tc_ld32(t_row + 128 + c0, u);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const float g = __uint_as_float(v[i]);
+                f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : epi_silu(g)) * __uint_as_float(u[i]);
+            }
+        } else {
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+        }
+        if (row < M) {
+            const int col = n0 + c0;
+            if (EPI == EPI_F32) {
+                float* dst = reinterpret_cast<float*>(c) + ((size_t)split * M + row) * ldc + col;
+                if (col + 32 <= n_cols && (ldc & 3) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+                } else {
+                    for (int i = 0; i < 32; ++i)
+                        if (col + i < n_cols) dst[i] = f[i];
+                }
+            } else {
+                bf16* dst = reinterpret_cast<bf16*>(c) + (size_t)row * ldc + col;
+                if (col + 32 <= n_cols && (ldc & 7) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 o;
+                        __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]), p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+                        __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]), p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+                        o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                        o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                        *reinterpret_cast<uint4*>(dst + i) = o;
+                    }
+                } else {
+                    for (int i = 0; i < 32; ++i)
+                        if (col + i < n_cols) dst[i] = __float2bfloat16_rn(f[i]);
+                }
+            }
+        }
+    }
+}
 
 template <int EPI, int AROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -183,59 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
-            const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-            const bool quarter_has_rows = m0 + quarter * 32 < M;     // the same for the whole warp
-#pragma unroll 1
-            for (int c0 = 0; c0 < tile_n && quarter_has_rows; c0 += 32) {
-                uint32_t v[32];
-                float f[32];
-                tc_ld32(t_row + c0, v);
-                if (GATED) {
-                    uint32_t u[32];
-                    tc_ld32(t_row + 128 + c0, u);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const float g = __uint_as_float(v[i]);
-                        f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : epi_silu(g)) * __uint_as_float(u[i]);
-                    }
-                } else {
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-                }
-                if (row < M) {
-                    const int col = n0 + c0;
-                    if (EPI == EPI_F32) {
-                        float* dst = reinterpret_cast<float*>(c) + ((size_t)split * M + row) * ldc + col;
-                        if (col + 32 <= n_cols && (ldc & 3) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 4)
-                                *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
-                        } else {
-                            for (int i = 0; i < 32; ++i)
-                                if (col + i < n_cols) dst[i] = f[i];
-                        }
-                    } else {
-                        bf16* dst = reinterpret_cast<bf16*>(c) + (size_t)row * ldc + col;
-                        if (col + 32 <= n_cols && (ldc & 7) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 o;
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]), p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]), p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
-                                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-                                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-                                *reinterpret_cast<uint4*>(dst + i) = o;
-                            }
-                        } else {
-                            for (int i = 0; i < 32; ++i)
-                                if (col + i < n_cols) dst[i] = __float2bfloat16_rn(f[i]);
-                        }
-                    }
-                }
-            }
+            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, split, m0, n0, tmem_base + acc * BN, quarter, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);   // this warp has drained its quarter
@@ -247,6 +260,167 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Two CTAs per tile.  A cluster of two CTAs (on neighbouring SMs) shares a 256 x 256 tile: each holds its
+// own 128 rows of A and ONE half of the W tile (128 of the 256 rows), and tcgen05.mma.cta_group::2, issued
+// by the first CTA for both, multiplies each CTA's A rows by both halves.  A stage is then 32 KB instead
+// of 48 KB per CTA, so the ring holds six stages, and each SM writes and reads a third less shared memory
+// per product.  Used when A has more than 128 rows.
+//   full[s]    lives in the first CTA; both producers announce their bytes there (two arrivals) and both
+//              CTAs' copies count on it (cp.async.bulk.tensor with cta_group::2);
+//   empty[s]   in each CTA; the issuer's tcgen05.commit arrives on both (commit multicast);
+//   tfull[a]   in each CTA, by the same multicast; tempty[a] in the first CTA, eight arrivals (the four
+//              epilogue warps of each CTA).
+// Both CTAs allocate and free tensor memory together (cta_group::2), and neither leaves before the other
+// has finished (cluster barrier): its shared memory and barriers are written by the other until then.
+// ------------------------------------------------------------------------------------------------
+struct PairRing {
+    static constexpr int STAGES = 6;
+    static constexpr int A_BYTES = 128 * BK * 2, B_BYTES = 128 * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 256;
+};
+constexpr uint32_t IDESC_PAIR = umma_idesc(2 * BM, BN, false, false);
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
+                    int ldc, int M, int N, int K, int up_row_offset, int k_splits, int* __restrict__ status) {
+    constexpr int STAGES = PairRing::STAGES, A_BYTES = PairRing::A_BYTES, STAGE_BYTES = PairRing::STAGE_BYTES;
+    constexpr int RING_BYTES = PairRing::RING_BYTES;
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t ring = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = ring + RING_BYTES;
+    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t tmem_slot = tempty0 + 16;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_addr(smem_raw)));
+
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    const int n_cols = GATED ? N / 2 : N;
+    const int tile_n = GATED ? 128 : BN;
+    const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (n_cols + tile_n - 1) / tile_n;
+    const int tiles_mn = tiles_m * tiles_n, num_tiles = tiles_mn * k_splits;
+    const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 2); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tc_alloc_pair(tmem_slot, 512);
+    tc_fence_before();
+    cluster_sync();                       // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+    const uint32_t lead_full0 = cluster_map(full0, 0), lead_tempty0 = cluster_map(tempty0, 0);
+    // this CTA's half of the W tile: rows n0.. (first CTA) or the second half / the up matrix (second CTA)
+    const int w_row_offset = rank == 0 ? 0 : (GATED ? up_row_offset : 128);
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one in each CTA) ----------------
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int early = 0;
+            if (pair < num_tiles) {                 // W tiles of the first stages before the predecessor has finished
+                const int mn = pair % tiles_mn, split = pair / tiles_mn;
+                const int n0 = (mn / tiles_m) * tile_n;
+                const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
+                early = min(STAGES, kb_hi - kb_lo);
+                for (int i = 0; i < early; ++i) {
+                    mbar_expect_tx_cluster(lead_full0 + 8 * i, STAGE_BYTES);
+                    tma_load_2d_pair(ring + i * STAGE_BYTES + A_BYTES, &map_w, lead_full0 + 8 * i, (kb_lo + i) * BK, n0 + w_row_offset);
+                }
+            }
+            pdl_wait();
+            int issued = 0;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+                const int mn = tile % tiles_mn, split = tile / tiles_mn;
+                const int m0 = (mn % tiles_m) * 2 * BM + (int)rank * BM, n0 = (mn / tiles_m) * tile_n;
+                const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
+                for (int kb = kb_lo; kb < kb_hi; ++kb, ++issued) {
+                    const uint32_t a_dst = ring + stage * STAGE_BYTES, b_dst = a_dst + A_BYTES, bar = lead_full0 + 8 * stage;
+                    if (issued < early) {
+                        tma_load_2d_pair(a_dst, &map_a, bar, kb * BK, m0);
+                    } else {
+                        if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
+                        mbar_expect_tx_cluster(bar, STAGE_BYTES);
+                        tma_load_2d_pair(a_dst, &map_a, bar, kb * BK, m0);
+                        tma_load_2d_pair(b_dst, &map_w, bar, kb * BK, n0 + w_row_offset);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) atomicExch(status, GAVE_UP_PRODUCER);
+            // stay until every filled stage has been consumed, or the limit passes
+            for (int s = 0; s < STAGES; ++s) {
+                if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) break;
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the first CTA's, for both ----------------
+        if (lane == 0 && rank == 0) {
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + acc * BN;
+                const int split = tile / tiles_mn;
+                const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
+                    if (!mbar_wait(full0 + 8 * stage, phase)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        tc_mma_pair(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), IDESC_PAIR,
+                                    (kb > kb_lo || k > 0) ? 1u : 0u);
+                    tc_commit_pair(empty0 + 8 * stage, 3);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit_pair(tfull0 + 8 * acc, 3);
+            }
+            if (!ok) atomicExch(status, GAVE_UP_MMA);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 of each CTA drain that CTA's 128 rows ----------------
+        pdl_wait();
+        const int quarter = warp & 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const int mn = tile % tiles_mn, split = tile / tiles_mn;
+            const int m0 = (mn % tiles_m) * 2 * BM + (int)rank * BM, n0 = (mn / tiles_m) * tile_n;
+            if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
+            tc_fence_after();
+            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, split, m0, n0, tmem_base + acc * BN, quarter, lane);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(tempty0 + 8 * acc);
+                else mbar_arrive_cluster(lead_tempty0 + 8 * acc);
+            }
+        }
+        if (!ok && lane == 0) atomicExch(status, GAVE_UP_EPILOGUE);
+    }
+    tc_fence_before();
+    cluster_sync();                       // nothing of either CTA is still in use by the other
+    if (warp == 1) {
+        tc_fence_after();
+        tc_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -321,6 +495,62 @@ static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, in
                        up_off, k_splits, status);
 }
 
+// How many pairs can be resident at once.  The kernel is persistent with a fixed stride over the tiles, so
+// a pair that only starts when another has left would double the time; not every SM need be part of a
+// pair that the hardware can form.
+template <int EPI>
+static int resident_pairs() {
+    static int pairs = -1;
+    if (pairs < 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * 148);
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = PairRing::SMEM_BYTES;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<EPI>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        pairs = n;
+    }
+    return pairs;
+}
+
+template <int EPI>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
+                       int k_splits, int* status, int pairs, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             PairRing::SMEM_BYTES);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        configured = true;
+    }
+    const int resident = resident_pairs<EPI>();
+    if (resident < 1) return WLLM_BAD_SIZE;
+    if (pairs > resident) pairs = resident;
+    return wllm_launch(gemm_tc_pair_kernel<EPI>, 2 * pairs, NUM_THREADS, PairRing::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
+                       up_off, k_splits, status);
+}
+
+// Number of CTA pairs of the two-CTA kernel that one device holds at once (for reports).
+WLLM_API int wllm_gemm_bf16_tc_resident_pairs() {
+    cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairRing::SMEM_BYTES);
+    return resident_pairs<EPI_BF16>();
+}
+
+// WLLM_GEMM_PAIR=0 keeps every product on the one-CTA kernel.
+static bool pair_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("WLLM_GEMM_PAIR");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
 static int a_rows_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 
 template <int EPI>
@@ -354,6 +584,17 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     r = tensor_map(w, N, K, ldw, 128, &mw);
     if (r) return r;
     const int n_cols = gated ? N / 2 : N, tile_n = gated ? 128 : BN;
+    if (M > BM && max_ctas >= 2 && pair_enabled()) {
+        const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((n_cols + tile_n - 1) / tile_n) * k_splits;
+        const int pairs = tiles < max_ctas / 2 ? tiles : max_ctas / 2;
+        switch (epilogue) {
+            case EPI_BF16: return launch_pair<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, 1, status, pairs, stream);
+            case EPI_F32: return launch_pair<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, status, pairs, stream);
+            case EPI_GATED_GELU: return launch_pair<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, pairs, stream);
+            case EPI_GATED_SILU: return launch_pair<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, pairs, stream);
+        }
+        return WLLM_BAD_SIZE;
+    }
     const int tiles = ((M + BM - 1) / BM) * ((n_cols + tile_n - 1) / tile_n) * k_splits;
     const int ctas = tiles < max_ctas ? tiles : max_ctas;
     switch (epilogue) {
