@@ -188,7 +188,7 @@ def e2e_run(cfg, args, page_size: int):
     total = context + args.warmup + args.steps + prefill_steps + 4
     llm = LLM(None, config=cfg, random_seed=1, dtype="bfloat16", block_size=page_size,
               num_blocks=args.batch * (-(-total // page_size)) + 1, chunked_prefill_tokens=2048,
-              max_num_seqs=max(args.batch, 8), cuda_graphs=not args.no_graphs)
+              max_num_seqs=max(args.batch, 8), cuda_graphs=not args.no_graphs, async_scheduling=True)
     g = torch.Generator().manual_seed(11)
     sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + prefill_steps + 2, ignore_eos=True)
     for _ in range(args.batch):
@@ -200,7 +200,7 @@ def e2e_run(cfg, args, page_size: int):
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        got = llm.step()
+        got = llm.step()       # launches this step, then reads the tokens of the step before (pipelined)
         assert len(got) == args.batch
     torch.cuda.synchronize()
     sec = (time.perf_counter() - t0) / args.steps
@@ -352,7 +352,7 @@ def main() -> int:
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": args.context, "page_size": ps, "prefill_tokens": T,
-                   "cuda_graphs": not args.no_graphs, "parallelism": "single-gpu",
+                   "cuda_graphs": not args.no_graphs, "e2e_async_scheduling": True, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2 (weights %.2f GB read every step)" % (weight_bytes / 1e9),
                    "peaks": pk["source"]},
         "prefill": prefill,

@@ -141,3 +141,38 @@ def test_captured_decode_steps_change_nothing(folders, dtype):
     outs = graphed.generate(prompts, sp)
     assert graphed.runner.graph_launches > 0
     assert [o.token_ids for o in outs] == [o.token_ids for o in plain_run]
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_pipelined_scheduling_changes_no_token(folders, graphs):
+    """Steps launched before the host has read the tokens of the step before (decode entries take their
+    token from the device): the same tokens as step by step, with stop ids, scarce pages and penalties."""
+    prompts = prompts_of("B", (5, 40, 77, 3), seed=6)
+    base = dict(temperature=0.9, seed=5, max_tokens=40)
+    free_run = llm(folders["B"], dtype="float32", block_size=32, num_blocks=24).generate(
+        prompts, SamplingParams(ignore_eos=True, **base))
+    stop = free_run[1].token_ids[17]
+    sps = [SamplingParams(ignore_eos=True, **base), SamplingParams(stop_token_ids=(stop,), **base),
+           SamplingParams(ignore_eos=True, repetition_penalty=1.2, **base), SamplingParams(max_tokens=1)]
+    kw = dict(dtype="float32", block_size=32, num_blocks=9, chunked_prefill_tokens=32, admission="optimistic",
+              cuda_graphs=graphs)
+    stepwise = llm(folders["B"], **kw).generate(prompts, sps)
+    engine = llm(folders["B"], async_scheduling=True, **kw)
+    piped = engine.generate(prompts, sps)
+    assert [o.token_ids for o in piped] == [o.token_ids for o in stepwise]
+    assert [o.finish_reason for o in piped] == [o.finish_reason for o in stepwise]
+    assert piped[1].finish_reason == "stop" and piped[1].token_ids[-1] == stop
+    assert [o.logprobs for o in piped] == [o.logprobs for o in stepwise]
+    assert engine.runner.cache.free_pages() == [9] and not engine.has_unfinished()
+    if graphs:
+        assert engine.runner.graph_launches > 0
+
+
+def test_pipelined_scheduling_bfloat16_against_plain(folders):
+    prompts = prompts_of("A", (7, 19, 33))
+    sp = SamplingParams(max_tokens=16, ignore_eos=True)
+    outs = llm(folders["A"], dtype="bfloat16", block_size=16, num_blocks=24, async_scheduling=True,
+               cuda_graphs=True).generate(prompts, sp)
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 16
+        check_against_plain("A", folders["A"], p, o.token_ids, sp, 0, 2e-2)

@@ -28,26 +28,45 @@ class FakeRunner:
         self.cache = CacheManager([CacheGroupSpec("all", 1, 1, 8)], page_size, pages, max_requests)
         self.model = FakeModel()
         self.batches = []
+        self.from_device = []      # per step: entries whose token came from the step before, unread by the host
 
-    def step(self, entries):
+    def step(self, entries, device_tokens=None):
         self.cache.reserve([(e.cache, len(e.tokens)) for e in entries])
         rows = []
         for e in entries:
+            tokens = list(e.tokens) if e.device_row is None else [device_tokens[e.device_row]]
             for w in e.want:
                 pos = e.cache.num_tokens + w
                 row = torch.zeros(VOCAB)
-                row[(e.tokens[w] * 7 + pos * 3 + 1) % VOCAB] = 1.0
+                row[(tokens[w] * 7 + pos * 3 + 1) % VOCAB] = 1.0
                 rows.append(row)
         self.batches.append([(e.cache.request_id, len(e.tokens), list(e.want)) for e in entries])
+        self.from_device.append(sum(e.device_row is not None for e in entries))
         for e in entries:
             self.cache.commit(e.cache, len(e.tokens))
         self.cache.check()
         return torch.stack(rows) if rows else torch.zeros(0, VOCAB)
 
 
+class Pending:
+    def __init__(self, tokens):
+        self.tokens_device, self.reads = tokens, 0
+
+    def get(self):
+        self.reads += 1
+        return self.tokens_device, [0.0] * len(self.tokens_device)
+
+
 class ArgmaxSampler:
+    def __init__(self):
+        self.seen_at_launch = []
+
     def sample(self, logits, params, counters, seeds, generated):
         return logits.argmax(-1).tolist(), [0.0] * logits.shape[0]
+
+    def sample_pending(self, logits, params, counters, seeds, generated):
+        self.seen_at_launch.append((list(counters), [set(g) for g in generated]))
+        return Pending(logits.argmax(-1).tolist())
 
 
 def expected_output(prompt, n):
@@ -203,3 +222,83 @@ def test_seeds_are_drawn_once_and_kept_over_preemption():
     seed_a = a.seed
     s.run_to_completion()
     assert b.seed == 1234 and a.seed == seed_a and b.preemptions >= 1
+
+
+# ---- pipelined scheduling: step k+1 is launched before the tokens of step k are read ----
+
+def run_both(make_requests, **kw):
+    out = []
+    for pipelined in (False, True):
+        s, runner = make(async_scheduling=pipelined, **kw)
+        rs = make_requests()
+        for r in rs:
+            s.add_request(r)
+        done = s.run_to_completion()
+        assert sorted(r.request_id for r in done) == sorted(r.request_id for r in rs)     # each finishes once
+        assert runner.cache.free_pages() == [kw.get("pages", 16)] and not s.has_unfinished()
+        out.append((s, runner, rs))
+    return out
+
+
+def test_pipelined_steps_take_tokens_from_the_device_and_give_the_same_outputs():
+    (s0, run0, plain), (s1, run1, piped) = run_both(lambda: [req(0, 5, 6), req(1, 9, 4), req(2, 3, 1)], pages=32)
+    for a, b in zip(plain, piped):
+        assert a.output_token_ids == b.output_token_ids == expected_output(a.prompt_token_ids, a.sampling.max_tokens)
+        assert a.finish_reason == b.finish_reason == "length"
+    assert sum(run0.from_device) == 0 and sum(run1.from_device) > 0
+    assert run1.batches == run0.batches                  # ends that are known by count waste no step
+    assert s1.stats["dropped_tokens"] == 0
+
+
+def test_pipelined_returns_the_tokens_of_the_step_before():
+    s, runner = make(async_scheduling=True)
+    a = req(0, 5, 4)
+    s.add_request(a)
+    assert s.step() == [] and a.inflight == 1 and a.output_token_ids == []      # sampled, not read yet
+    assert s.step() == [a] and len(a.output_token_ids) == 1 and a.inflight == 1
+    assert runner.from_device == [0, 1]
+    s.run_to_completion()
+    assert a.output_token_ids == expected_output(a.prompt_token_ids, 4)
+
+
+def test_pipelined_stop_token_costs_one_dropped_token_and_frees_the_pages():
+    first = expected_output(req(0, 4).prompt_token_ids, 3)
+    (s0, run0, plain), (s1, run1, piped) = run_both(
+        lambda: [Request(0, req(0, 4).prompt_token_ids, SamplingParams(max_tokens=10, stop_token_ids=(first[1],))),
+                 req(1, 6, 5)], pages=16)
+    assert plain[0].output_token_ids == piped[0].output_token_ids == first[:2] and piped[0].finish_reason == "stop"
+    assert plain[1].output_token_ids == piped[1].output_token_ids
+    assert s1.stats["dropped_tokens"] == 1 and s0.stats["dropped_tokens"] == 0
+    ran = [sum(1 for rid, _, _ in b if rid == 0) for b in run1.batches]
+    assert sum(ran) == sum(1 for b in run0.batches for rid, _, _ in b if rid == 0) + 1   # it ran once more
+
+
+def test_pipelined_with_budget_preemption_and_late_arrivals():
+    def requests():
+        return [req(0, 7, 9), req(1, 6, 9), req(2, 11, 3)]
+    (s0, _, plain), (s1, run1, piped) = run_both(requests, pages=7, budget=5, admission="optimistic")
+    assert s1.stats["preemptions"] >= 1
+    for a, b in zip(plain, piped):
+        assert a.output_token_ids == b.output_token_ids == expected_output(a.prompt_token_ids, a.sampling.max_tokens)
+
+
+def test_pipelined_repetition_penalty_sees_every_earlier_token():
+    s, _ = make(async_scheduling=True)
+    a = Request(0, [3, 4, 5], SamplingParams(max_tokens=4, repetition_penalty=1.3))
+    s.add_request(a)
+    s.run_to_completion()
+    assert a.output_token_ids == expected_output(a.prompt_token_ids, 4)
+    for counters, seen in s.sampler.seen_at_launch:
+        assert len(seen[0]) == len(set(a.output_token_ids[:counters[0]]))   # nothing in flight when it is sampled
+
+
+def test_pipelined_cancel_with_a_token_in_flight():
+    s, runner = make(async_scheduling=True)
+    a, b = req(0, 5, 6), req(1, 4, 6)
+    s.add_request(a); s.add_request(b)
+    s.step(); s.step()
+    assert a.inflight == 1 and s.cancel(0)
+    s.run_to_completion()
+    assert a.finish_reason == "cancelled" and len(a.output_token_ids) == 1
+    assert b.output_token_ids == expected_output(b.prompt_token_ids, 6)
+    assert runner.cache.free_pages() == [16] and s.stats["dropped_tokens"] == 1

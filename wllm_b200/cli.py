@@ -27,6 +27,8 @@ def parser() -> argparse.ArgumentParser:
     ap.add_argument("--block-size", type=int, default=16)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--cuda-graphs", action="store_true", help="replay captured CUDA graphs for decode steps")
+    ap.add_argument("--async-scheduling", action="store_true",
+                    help="launch each step before the host has read the tokens of the step before")
     ap.add_argument("--chunked-prefill-tokens", type=int, default=None,
                     help="max prompt tokens processed per scheduler step (enables chunked prefill)")
     ap.add_argument("--max-num-seqs", type=int, default=256, help="requests that may be live at once")
@@ -72,7 +74,8 @@ def main(argv=None) -> int:
     from . import LLM, SamplingParams
     llm = LLM(args.model, dtype=args.dtype, block_size=args.block_size, num_blocks=args.num_blocks,
               chunked_prefill_tokens=args.chunked_prefill_tokens, max_num_seqs=args.max_num_seqs,
-              cuda_graphs=args.cuda_graphs, device="cuda:0", admission=args.admission)
+              cuda_graphs=args.cuda_graphs, device="cuda:0", admission=args.admission,
+              async_scheduling=args.async_scheduling)
     prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.prompt_ids]
     if args.prompt_lens:
         import torch

@@ -1,6 +1,20 @@
 // Scaled embedding gather: out[n, :] = float(table[ids[n], :]) * scale, written to the
 // 32-bit residual stream.  One block per token, 16-byte loads where the row allows.
+// And the patch that lets a step start before the host has seen the previous step's tokens:
+// ids[dst[i]] = sampled[src[i]], device to device.
 #include "common.cuh"
+
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst, const int* __restrict__ sampled,
+                                    const int* __restrict__ src, int n) {
+    pdl_begin();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) ids[dst[i]] = sampled[src[i]];
+}
+
+WLLM_API int wllm_patch_tokens(int* ids, const int* dst, const int* sampled, const int* src, int n, cudaStream_t stream) {
+    if (n <= 0) return WLLM_OK;
+    return wllm_launch(patch_tokens_kernel, (n + 127) / 128, 128, 0, stream, ids, dst, sampled, src, n);
+}
 
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table, float scale,

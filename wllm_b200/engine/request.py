@@ -31,6 +31,8 @@ class Request:
     num_computed: int = 0         # tokens whose keys and values are in the cache
     preemptions: int = 0
     seen: set = field(default_factory=set)   # distinct generated ids, for the repetition penalty
+    inflight: int = 0             # 1 while its newest token is sampled on the device and not yet read
+    inflight_row: int = -1        # that token's row among the sampled tokens of the step before
 
     @property
     def num_tokens(self) -> int:

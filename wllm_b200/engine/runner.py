@@ -30,6 +30,9 @@ class StepEntry:
     cache: RequestCache
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    # The entry's single token is not known on the host yet: it is row `device_row` of the `device_tokens`
+    # given to `step` (what the sampler left on the device); `tokens` then holds one placeholder.
+    device_row: int | None = None
 
 
 SM_COUNT = 148   # B200
@@ -113,7 +116,7 @@ class ModelRunner:
         return buf[:n].view(shape)
 
     # -- batch building --------------------------------------------------------------
-    def _build(self, entries: list, table_width: int | None = None) -> StepContext:
+    def _build(self, entries: list, table_width: int | None = None, device_tokens=None) -> StepContext:
         cache, ps = self.cache, self.cache.page_size
         G, R = len(cache.groups), len(entries)
         lens = [len(e.tokens) for e in entries]
@@ -125,7 +128,7 @@ class ModelRunner:
             return (n + 3) & ~3
         sizes = [("token_ids", N), ("positions", N), ("token_req", N)] + [(f"slots{g}", N) for g in range(G)] + \
                 [("req_q_start", R), ("req_q_len", R), ("req_ctx_len", R), ("req_slot", R), ("want_rows", M)] + \
-                [(f"table{g}", R * P) for g in range(G)]
+                [(f"table{g}", R * P) for g in range(G)] + [("patch_dst", R), ("patch_src", R)]
         offsets, total = {}, 0
         for name, n in sizes:
             offsets[name] = (total, n)
@@ -174,6 +177,11 @@ class ModelRunner:
             wants.extend(start + w for w in e.want)
             start += n
         view("want_rows")[:] = wants
+        patches = [(r, e.device_row) for r, e in enumerate(entries) if e.device_row is not None]
+        if patches:
+            starts = np.cumsum([0] + lens[:-1])
+            view("patch_dst")[:len(patches)] = [starts[r] for r, _ in patches]
+            view("patch_src")[:len(patches)] = [row for _, row in patches]
 
         if self._meta is None or self._meta.numel() < total:
             cap = max(total, 4096, 2 * (self._meta.numel() if self._meta is not None else 0))
@@ -199,6 +207,9 @@ class ModelRunner:
         ctx.req_ctx_len, ctx.req_slot, ctx.want_rows = dev("req_ctx_len"), dev("req_slot"), dev("want_rows")
         ctx.group_slots = [dev(f"slots{g}") for g in range(G)]
         ctx.group_tables = [dev(f"table{g}").view(R, P) for g in range(G)]
+        if patches:
+            ops.patch_tokens(ctx.token_ids, dev("patch_dst")[:len(patches)], device_tokens,
+                             dev("patch_src")[:len(patches)])
         return ctx
 
     def _table_copy(self, rc, group: int) -> np.ndarray:
@@ -227,6 +238,8 @@ class ModelRunner:
             if e.cache.num_tokens + n > limit:
                 raise ValueError(f"request {e.cache.request_id!r}: {e.cache.num_tokens + n} tokens exceed the "
                                  f"model's {limit} positions")
+            if e.device_row is not None and n != 1:
+                raise ValueError(f"request {e.cache.request_id!r}: a token taken from the device stands alone")
             lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"request {e.cache.request_id!r}: token id {lo if lo < 0 else hi} outside the "
@@ -247,13 +260,13 @@ class ModelRunner:
     def _graphable(self, entries: list) -> bool:
         return self._graphs_on and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
-    def _forward_graph(self, entries: list) -> torch.Tensor:
+    def _forward_graph(self, entries: list, device_tokens=None) -> torch.Tensor:
         widest = max(1, max(len(t) for e in entries for t in e.cache.tables))
         width = 8
         while width < widest:
             width *= 2
         key = (len(entries), width)
-        ctx = self._build(entries, table_width=width)
+        ctx = self._build(entries, table_width=width, device_tokens=device_tokens)
         rec = self._graphs.get(key)
         if rec is None:
             arena, saved = {}, self._arena
@@ -277,18 +290,21 @@ class ModelRunner:
 
     # -- the step ----------------------------------------------------------------------
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """`device_tokens`: int32 tokens on the device, read by the entries that name a `device_row`."""
         entries = list(entries)
         if not entries:
             return torch.empty((0, self.model.plan.vocab_size), dtype=torch.float32, device=self.device)
         self._validate(entries)
+        if device_tokens is None and any(e.device_row is not None for e in entries):
+            raise ValueError("an entry names a device row, but no device tokens were given")
         self.cache.reserve([(e.cache, len(e.tokens)) for e in entries])   # all or nothing
         try:
             if self._graphable(entries):
-                logits = self._forward_graph(entries)
+                logits = self._forward_graph(entries, device_tokens)
                 ctx = None
             else:
-                ctx = self._build(entries)
+                ctx = self._build(entries, device_tokens=device_tokens)
                 logits = self.model.forward(ctx)
         except BaseException:
             for e in entries:          # a failed step holds no pages beyond its committed tokens

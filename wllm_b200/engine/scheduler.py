@@ -25,6 +25,16 @@ Policy, with the reference's rule beside it:
               not run even alone is refused when it is added, so the loop cannot spin.
   finishing   end-of-sequence id, stop ids, max_tokens or the model's length; pages are
               given back in the same step (scheduler.py:492-495).
+  pipelining  `async_scheduling` (no counterpart in the reference): step k+1 is planned and
+              launched before the host has read the tokens of step k.  Its decode entries
+              take their token from the device, where the sampler left it; the host reads
+              step k's tokens while step k+1 runs, so `step()` returns the tokens of the
+              step before.  A request that turns out to have stopped at step k has then
+              already run in step k+1: that token is dropped, its pages are given back
+              (the device runs in stream order, so whoever gets them writes later).
+              max_tokens and the model's length are known by count and waste nothing.
+              A repetition penalty needs every earlier token on the host, and a shortage
+              of pages is settled with nothing in flight: both read the tokens first.
 """
 from __future__ import annotations
 
@@ -38,7 +48,8 @@ from .runner import StepEntry
 
 class Scheduler:
     def __init__(self, runner, sampler, chunked_prefill_tokens: int | None = None, max_num_seqs: int = 256,
-                 max_model_len: int | None = None, admission: str = "worst_case", seed: int = 0):
+                 max_model_len: int | None = None, admission: str = "worst_case", seed: int = 0,
+                 async_scheduling: bool = False):
         if admission not in ("worst_case", "optimistic"):
             raise ValueError("admission must be 'worst_case' or 'optimistic'")
         self.runner, self.sampler, self.cache = runner, sampler, runner.cache
@@ -49,7 +60,10 @@ class Scheduler:
         self.waiting: list = []
         self.live: list = []          # admitted requests in order of admission
         self._rng = random.Random(seed)
-        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "finished": 0}
+        self.async_scheduling = async_scheduling
+        self._inflight = None         # (PendingSample, [(request, keep)]) of the step whose tokens are unread
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "finished": 0,
+                      "dropped_tokens": 0}
 
     # -- requests ------------------------------------------------------------------------
     def _pages(self, tokens: int) -> int:
@@ -76,7 +90,7 @@ class Scheduler:
         self.waiting.append(request)
 
     def has_unfinished(self) -> bool:
-        return bool(self.waiting or self.live)
+        return bool(self.waiting or self.live or self._inflight)
 
     def cancel(self, request_id) -> bool:
         """Stop a request wherever it is and give back what it holds (scheduler.py:158-176)."""
@@ -98,6 +112,7 @@ class Scheduler:
             self.cache.close(r.cache)
             r.cache = None
         r.num_computed = 0
+        r.inflight = 0
 
     # -- admission -------------------------------------------------------------------------
     def _pledged(self) -> int:
@@ -132,8 +147,11 @@ class Scheduler:
         budget = self.budget if self.budget is not None else 1 << 60
         plan, taken = [], 0
         for r in self.live:
-            left = r.num_tokens - r.num_computed
+            left = r.num_tokens + r.inflight - r.num_computed
             if r.status == RequestStatus.RUNNING:
+                if r.inflight and (len(r.output_token_ids) + 1 >= r.sampling.max_tokens
+                                   or r.num_tokens + 1 >= self.max_model_len):
+                    continue                               # the token in flight is its last
                 plan.append((r, r.num_computed, left))     # its newest token (one), outside the budget
                 continue
             if budget <= 0:
@@ -158,20 +176,62 @@ class Scheduler:
             taken += self._pages(c)
         return plan
 
+    def _resolve(self) -> list:
+        """Read the tokens of the step in flight and give them to their requests; finish and free."""
+        if self._inflight is None:
+            return []
+        pending, rows = self._inflight
+        self._inflight = None
+        tokens, logprobs = pending.get()
+        got = []
+        for (r, keep), t, lp in zip(rows, tokens, logprobs):
+            if not keep or r.finished or r.inflight == 0:
+                self.stats["dropped_tokens"] += 1
+                continue
+            r.inflight = 0
+            r.append_token(int(t), float(lp), self.max_model_len)
+            got.append(r)
+        self._finish()
+        return got
+
+    def _finish(self) -> None:
+        for r in [r for r in self.live if r.finished]:
+            self._release(r)
+            self.live.remove(r)
+            self.stats["finished"] += 1
+
+    def _entry(self, r: Request, start: int, c: int) -> StepEntry:
+        want = [c - 1] if start + c == r.num_tokens + r.inflight else []
+        if r.inflight:
+            return StepEntry(r.cache, [0], want, device_row=r.inflight_row)
+        return StepEntry(r.cache, r.tokens(start, start + c), want)
+
     def step(self) -> list:
-        """One batch.  Returns the requests that got a token in this step."""
+        """One batch.  Returns the requests that got a token on the host in this call: those sampled in this
+        step, or with `async_scheduling` those of the step before."""
+        got = []
+        if self._inflight and any(r.sampling.repetition_penalty != 1.0 for r in self.live):
+            got += self._resolve()
         plan = self._plan()
         while True:
             if not plan:
+                if self._inflight:
+                    return self._once(got + self._resolve())
                 if self.waiting and not self.live:
                     raise RuntimeError(f"request {self.waiting[0].request_id!r} cannot be admitted into an empty engine")
-                return []
-            entries = [StepEntry(r.cache, r.tokens(start, start + c), [c - 1] if start + c == r.num_tokens else [])
-                       for r, start, c in plan]
+                return got
+            entries = [self._entry(r, start, c) for r, start, c in plan]
             try:
-                logits = self.runner.step(entries)
+                if self._inflight:
+                    logits = self.runner.step(entries, device_tokens=self._inflight[0].tokens_device)
+                else:
+                    logits = self.runner.step(entries)
                 break
             except OutOfPages:
+                if self._inflight:            # settle it with every token on the host
+                    got += self._resolve()
+                    plan = self._plan()
+                    continue
                 if len(self.live) <= 1:
                     raise
                 victim = self._preempt_youngest()
@@ -184,20 +244,40 @@ class Scheduler:
             else:
                 self.stats["prefill_tokens"] += c
             r.num_computed = start + c
-            if r.num_computed == r.num_tokens:
+            if r.num_computed == r.num_tokens + r.inflight:
                 sampled.append(r)
-        if sampled:
-            tokens, logprobs = self.sampler.sample(
-                logits, [r.sampling for r in sampled], [len(r.output_token_ids) for r in sampled],
+        args = ([r.sampling for r in sampled], [len(r.output_token_ids) + r.inflight for r in sampled],
                 [r.seed for r in sampled], [r.seen for r in sampled])
-            for r, t, lp in zip(sampled, tokens, logprobs):
-                r.status = RequestStatus.RUNNING
-                r.append_token(int(t), float(lp), self.max_model_len)
-        for r in [r for r in self.live if r.finished]:
-            self._release(r)
-            self.live.remove(r)
-            self.stats["finished"] += 1
-        return sampled
+        if not self.async_scheduling:
+            if sampled:
+                tokens, logprobs = self.sampler.sample(logits, *args)
+                for r, t, lp in zip(sampled, tokens, logprobs):
+                    r.status = RequestStatus.RUNNING
+                    r.append_token(int(t), float(lp), self.max_model_len)
+            self._finish()
+            return sampled
+        pending = self.sampler.sample_pending(logits, *args) if sampled else None
+        got += self._resolve()                 # the step before, while this one runs
+        if pending is not None:
+            rows = []
+            for row, r in enumerate(sampled):
+                keep = not r.finished          # it may just have turned out to have stopped a step ago
+                if keep:
+                    r.status, r.inflight, r.inflight_row = RequestStatus.RUNNING, 1, row
+                rows.append((r, keep))
+            self._inflight = (pending, rows)
+            if any(r.sampling.repetition_penalty != 1.0 for r in sampled):
+                got += self._resolve()
+        return self._once(got)
+
+    @staticmethod
+    def _once(requests: list) -> list:
+        seen, out = set(), []
+        for r in requests:
+            if id(r) not in seen:
+                seen.add(id(r))
+                out.append(r)
+        return out
 
     def run_to_completion(self, max_steps: int | None = None) -> list:
         """Step until nothing is left (scheduler.py:500-506); returns finished requests in finishing order."""

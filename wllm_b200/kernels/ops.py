@@ -79,6 +79,17 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, scale: float, out: torc
     return out
 
 
+def patch_tokens(ids: torch.Tensor, dst: torch.Tensor, sampled: torch.Tensor, src: torch.Tensor) -> None:
+    """ids[dst[i]] = sampled[src[i]] on the device: tokens that the previous step sampled and the host has
+    not read yet become inputs of this step."""
+    _need_cuda(ids, dst, sampled, src)
+    n = dst.shape[0]
+    assert src.shape[0] == n
+    lib = load_family("embedding")
+    _check(lib.wllm_patch_tokens(_ptr(_int32(ids, "ids")), _ptr(_int32(dst, "dst")), _ptr(_int32(sampled, "sampled")),
+                                 _ptr(_int32(src, "src")), n, _stream()), "patch_tokens")
+
+
 def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset: float, out: torch.Tensor,
             rows=None, delta_splits: int = 0) -> torch.Tensor:
     """Fold `delta` into the residual (when given), then norm: see csrc/norm.cu.  With `delta_splits` = S > 0,

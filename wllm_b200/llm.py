@@ -37,7 +37,8 @@ class LLM:
     def __init__(self, model: str | None = None, *, config=None, random_seed: int | None = None,
                  dtype="bfloat16", block_size: int = 16, num_blocks: int = 256,
                  chunked_prefill_tokens: int | None = None, max_num_seqs: int = 256, max_model_len: int | None = None,
-                 cuda_graphs: bool = False, device: str = "cuda:0", admission: str = "worst_case", seed: int = 0):
+                 cuda_graphs: bool = False, device: str = "cuda:0", admission: str = "worst_case", seed: int = 0,
+                 async_scheduling: bool = False):
         """`model`: a folder with config.json and model.safetensors.  Without it, `config` (a typed
         configuration) and `random_seed` make a model with random weights on the device."""
         self.engine_config = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=num_blocks,
@@ -50,7 +51,8 @@ class LLM:
             self.runner.enable_graphs()
         self.sampler = Sampler(ec.device)
         self.scheduler = Scheduler(self.runner, self.sampler, chunked_prefill_tokens=chunked_prefill_tokens,
-                                   max_num_seqs=max_num_seqs, max_model_len=max_model_len, admission=admission, seed=seed)
+                                   max_num_seqs=max_num_seqs, max_model_len=max_model_len, admission=admission, seed=seed,
+                                   async_scheduling=async_scheduling)
         self.eos_token_id = self.model.plan.eos_token_id
         self._next_id = 0
 
@@ -64,7 +66,8 @@ class LLM:
         return req
 
     def step(self) -> list:
-        """One scheduler step; returns the requests that got a token."""
+        """One scheduler step; returns the requests that got a token (with `async_scheduling`: the tokens of
+        the step before, read while this one runs)."""
         return self.scheduler.step()
 
     def has_unfinished(self) -> bool:

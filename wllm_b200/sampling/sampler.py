@@ -18,11 +18,28 @@ from ..engine.staging import PinnedRing
 from .params import SamplingParams
 
 
+class PendingSample:
+    """The sampling of one step, enqueued: its tokens lie on the device (`tokens_device`, valid until the
+    sampler's next launch) and are on their way to pinned host memory; `get()` waits for them."""
+
+    def __init__(self, rows: int, tokens_device, host: torch.Tensor | None, event):
+        self.rows, self.tokens_device, self._host, self._event = rows, tokens_device, host, event
+
+    def get(self):
+        if self.rows == 0:
+            return [], []
+        self._event.synchronize()
+        out = self._host[:2 * self.rows].numpy()
+        return out[:self.rows].tolist(), out[self.rows:].view(np.float32).tolist()
+
+
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
         self._ring = PinnedRing(self.device)
-        self._dev = self._out = self._out_host = None
+        self._dev = self._out = None
+        self._out_hosts = [None, None]   # two pinned result buffers: one is read while the next step fills the other
+        self._turn = 0
         self._stats = None               # per-chunk (max, arg-max, sum) of the greedy path
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -31,23 +48,30 @@ class Sampler:
         """logits [rows, vocab] float32 on the device; params[i]: SamplingParams; counters[i]: index of
         the output token being drawn; seeds[i]: the request's 64-bit seed; generated[i]: its distinct
         generated ids (read only when its repetition penalty is not 1).  Returns (tokens, logprobs) lists."""
+        return self.sample_pending(logits, params, counters, seeds, generated).get()
+
+    def sample_pending(self, logits: torch.Tensor, params: list, counters: list, seeds: list, generated: list):
+        """As `sample`, without waiting: returns a PendingSample.  At most two may be outstanding (the result
+        buffers alternate), and one's `tokens_device` is overwritten by the launch after it."""
         rows = logits.shape[0]
         if rows == 0:
-            return [], []
-        self.launch(logits, params, counters, seeds, generated)
-        self._out_host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            return PendingSample(0, None, None, None)
+        tokens = self.launch(logits, params, counters, seeds, generated)
+        self._turn ^= 1
+        host = self._out_hosts[self._turn]
+        if host is None or host.numel() < 2 * rows:
+            host = self._out_hosts[self._turn] = torch.empty(max(2 * rows, 1024), dtype=torch.int32).pin_memory()
+        host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
         self.d2h_bytes = 8 * rows
-        out = self._out_host[:2 * rows].numpy()
-        return out[:rows].tolist(), out[rows:].view(np.float32).tolist()
+        return PendingSample(rows, tokens, host, event)
 
     def _launch_greedy(self, logits: torch.Tensor) -> torch.Tensor:
         """All rows greedy and unpenalised: no options to send; arg-max and log-sum-exp by 32 blocks a row."""
         rows, V = logits.shape
         if self._out is None or self._out.numel() < 2 * rows:
-            cap = max(2 * rows, 1024)
-            self._out = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._out_host = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._out = torch.empty(max(2 * rows, 1024), dtype=torch.int32, device=self.device)
         if self._stats is None or self._stats.numel() < rows * 96:
             self._stats = torch.empty(max(rows, 64) * 96, dtype=torch.float32, device=self.device)
         lib = load_family("sampling")
@@ -87,9 +111,7 @@ class Sampler:
         if self._dev is None or self._dev.numel() < total:
             self._dev = torch.empty(max(total, 8192), dtype=torch.int32, device=self.device)
         if self._out is None or self._out.numel() < 2 * rows:
-            cap = max(2 * rows, 1024)
-            self._out = torch.empty(cap, dtype=torch.int32, device=self.device)
-            self._out_host = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._out = torch.empty(max(2 * rows, 1024), dtype=torch.int32, device=self.device)
         self._ring.send(host, self._dev)
         base = self._dev.data_ptr()
 
