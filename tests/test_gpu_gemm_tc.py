@@ -92,3 +92,46 @@ def test_split_k_partial_sums(M, N, K):
     again = torch.empty_like(out)
     ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), out=again if parts > 1 else again[0], epilogue="f32", k_splits=parts)
     assert torch.equal(again, out)        # part s is the same sum whoever computes it
+
+
+@pytest.mark.parametrize("M,half", [(8, 48), (8, 64), (8, 112), (40, 32), (64, 80), (100, 16), (128, 96), (31, 128)])
+@pytest.mark.parametrize("epilogue", ["f32", "bf16", "gelu_tanh"])
+def test_every_tile_shape_of_products_of_few_rows(M, half, epilogue):
+    """The W tile of a stage is two halves of `half` rows: every multiple of 16 the row count allows, at an N
+    and K that are multiples of nothing."""
+    from wllm_b200.kernels import ops
+    I, K = 300, 200
+    a, w = operands(M, 2 * I, K, seed=half + M)
+    want = a.double() @ w.double().T
+    if epilogue == "gelu_tanh":
+        a, w = (a * 0.3).to(torch.bfloat16), (w * 0.3).to(torch.bfloat16)
+        want = torch.nn.functional.gelu(a.double() @ w[:I].double().T, approximate="tanh") * (a.double() @ w[I:].double().T)
+    got = ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), epilogue=epilogue, half_rows=half)
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0 and got.shape == want.shape
+    if epilogue == "f32":
+        torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-3 * math.sqrt(K))
+        assert torch.equal(got, ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), epilogue="f32", half_rows=128 if M > 32 else 48))
+    else:
+        torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+def test_a_tile_too_small_for_the_row_count_is_refused():
+    from wllm_b200.kernels import KernelError, ops
+    a, w = operands(8, 256, 64, seed=1)
+    with pytest.raises(KernelError):
+        ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), half_rows=32)      # 32 rows of A + 2 x 32 of W < the 128 rows read at A
+    with pytest.raises(KernelError):
+        ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), half_rows=40)
+
+
+def test_tile_plan_fills_the_sms():
+    from wllm_b200.kernels import ops
+    for M, N, K, gated, split in [(8, 2560, 2048, False, True), (8, 2048, 16384, False, True), (8, 32768, 2048, True, False),
+                                  (64, 2048, 2048, False, True), (1, 512, 200, False, True), (33, 300, 1024, False, True)]:
+        half, parts = ops.tile_plan(M, N, K, gated, split)
+        assert half % 16 == 0 and 16 <= half <= 128 and 1 <= parts <= 16
+        assert half >= (48 if M <= 32 else 32 if M <= 64 else 16)
+        kblocks = -(-K // 64)
+        assert -(-kblocks // parts) * (parts - 1) < kblocks       # no empty part
+    assert ops.tile_plan(8, 32768, 2048, True, False) == (112, 1)       # 147 tiles for 148 SMs

@@ -29,11 +29,14 @@ constexpr int B_HALF_BYTES = 128 * BK * 2, B_BYTES = 2 * B_HALF_BYTES;
 // 128 rows from that address, and the rows past AROWS (whatever lies behind in shared memory) only reach
 // accumulator rows that are never stored.  The smaller stage buys a deeper ring: more weight bytes in
 // flight per SM, which is what a step bound by streaming the weights needs.
+// The W tile of a stage is two halves of `half_rows` rows (a multiple of 16, at most 128): rows n.. and
+// n + half_rows.. of W, or the same rows of the gate and of the up matrix.  The host picks half_rows so that
+// the tiles (times the parts of K) fill the SMs evenly; smaller halves make the stages smaller and the ring
+// deeper (the stage count is fixed at launch from the ring's bytes).
 template <int AROWS> struct Ring {
-    static constexpr int STAGES = AROWS == 128 ? 4 : (AROWS == 64 ? 5 : 6);
     static constexpr int A_BYTES = AROWS * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int RING_BYTES = (AROWS == 128 ? 4 : (AROWS == 64 ? 5 : 6)) * (A_BYTES + B_BYTES);
+    static constexpr int MAX_STAGES = 12;
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 };
 constexpr int NUM_THREADS = 192;
@@ -49,7 +52,6 @@ enum { EPI_BF16 = 0, EPI_F32 = 1, EPI_GATED_GELU = 2, EPI_GATED_SILU = 3 };
 // status codes written by a role that gave up waiting
 enum { GAVE_UP_PRODUCER = 11, GAVE_UP_MMA = 12, GAVE_UP_EPILOGUE = 13 };
 
-constexpr uint32_t IDESC = umma_idesc(BM, BN, false, false);      // both operands K-major
 
 // gelu_tanh(x) = x/2 (1 + tanh u) = x / (1 + e^(-2u)),  u = sqrt(2/pi) (x + 0.044715 x^3): one exponential
 // and one division instead of a tanh.
@@ -59,79 +61,84 @@ __device__ __forceinline__ float epi_gelu(float x) {
 }
 __device__ __forceinline__ float epi_silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
-// Epilogue of one warp for one tile: reads its 32 lanes of the accumulator at t_acc (tile_n columns; for the
-// gated epilogues gate in columns 0-127 and up in 128-255), applies the epilogue and stores rows m0 + 32 *
-// quarter + lane of C.
-template <int EPI>
-__device__ __forceinline__ void drain_accumulator(void* __restrict__ c, int ldc, int M, int n_cols, int tile_n, int split, int m0,
-                                                  int n0, uint32_t t_acc, int quarter, int lane) {
+// Epilogue of one warp for one tile: reads its 32 lanes of the accumulator at t_acc (tile_n columns, a
+// multiple of 16; for the gated epilogues gate in columns 0.. and up from column up_col), applies the
+// epilogue and stores rows m0 + 32 * quarter + lane of C.
+template <int EPI, int W>
+__device__ __forceinline__ void drain_chunk(void* __restrict__ c, int ldc, int M, int n_cols, int split, int row, int col,
+                                            uint32_t t_chunk, uint32_t up_col) {
     constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
-    const int row = m0 + quarter * 32 + lane;
-    const uint32_t t_row = t_acc + ((uint32_t)(quarter * 32) << 16);
-    const bool quarter_has_rows = m0 + quarter * 32 < M;     // the same for the whole warp
-#pragma unroll 1
-    for (int c0 = 0; c0 < tile_n && quarter_has_rows; c0 += 32) {
-        uint32_t v[32];
-        float f[32];
-        tc_ld32(t_row + c0, v);
-        if (GATED) {
-            uint32_t u[32];
-            tc_ld32(t_row + 128 + c0, u);
-            tc_wait_ld();
+    uint32_t v[W];
+    float f[W];
+    tc_ld<W>(t_chunk, v);
+    if (GATED) {
+        uint32_t u[W];
+        tc_ld<W>(t_chunk + up_col, u);
+        tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float g = __uint_as_float(v[i]);
-                f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : epi_silu(g)) * __uint_as_float(u[i]);
+        for (int i = 0; i < W; ++i) {
+            const float g = __uint_as_float(v[i]);
+            f[i] = (EPI == EPI_GATED_GELU ? epi_gelu(g) : epi_silu(g)) * __uint_as_float(u[i]);
+        }
+    } else {
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < W; ++i) f[i] = __uint_as_float(v[i]);
+    }
+    if (row >= M) return;
+    if (EPI == EPI_F32) {
+        float* dst = reinterpret_cast<float*>(c) + ((size_t)split * M + row) * ldc + col;
+        if (col + W <= n_cols && (ldc & 3) == 0) {
+#pragma unroll
+            for (int i = 0; i < W; i += 4)
+                *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+        } else {
+            for (int i = 0; i < W; ++i)
+                if (col + i < n_cols) dst[i] = f[i];
+        }
+    } else {
+        bf16* dst = reinterpret_cast<bf16*>(c) + (size_t)row * ldc + col;
+        if (col + W <= n_cols && (ldc & 7) == 0) {
+#pragma unroll
+            for (int i = 0; i < W; i += 8) {
+                uint4 o;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]), p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]), p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
+                o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                *reinterpret_cast<uint4*>(dst + i) = o;
             }
         } else {
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-        }
-        if (row < M) {
-            const int col = n0 + c0;
-            if (EPI == EPI_F32) {
-                float* dst = reinterpret_cast<float*>(c) + ((size_t)split * M + row) * ldc + col;
-                if (col + 32 <= n_cols && (ldc & 3) == 0) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4)
-                        *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
-                } else {
-                    for (int i = 0; i < 32; ++i)
-                        if (col + i < n_cols) dst[i] = f[i];
-                }
-            } else {
-                bf16* dst = reinterpret_cast<bf16*>(c) + (size_t)row * ldc + col;
-                if (col + 32 <= n_cols && (ldc & 7) == 0) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 o;
-                        __nv_bfloat162 p0 = __floats2bfloat162_rn(f[i], f[i + 1]), p1 = __floats2bfloat162_rn(f[i + 2], f[i + 3]);
-                        __nv_bfloat162 p2 = __floats2bfloat162_rn(f[i + 4], f[i + 5]), p3 = __floats2bfloat162_rn(f[i + 6], f[i + 7]);
-                        o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-                        o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-                        *reinterpret_cast<uint4*>(dst + i) = o;
-                    }
-                } else {
-                    for (int i = 0; i < 32; ++i)
-                        if (col + i < n_cols) dst[i] = __float2bfloat16_rn(f[i]);
-                }
-            }
+            for (int i = 0; i < W; ++i)
+                if (col + i < n_cols) dst[i] = __float2bfloat16_rn(f[i]);
         }
     }
+}
+
+template <int EPI>
+__device__ __forceinline__ void drain_accumulator(void* __restrict__ c, int ldc, int M, int n_cols, int tile_n, int up_col,
+                                                  int split, int m0, int n0, uint32_t t_acc, int quarter, int lane) {
+    const int row = m0 + quarter * 32 + lane;
+    const uint32_t t_row = t_acc + ((uint32_t)(quarter * 32) << 16);
+    if (m0 + quarter * 32 >= M) return;                      // the same for the whole warp
+    int c0 = 0;
+#pragma unroll 1
+    for (; c0 + 32 <= tile_n; c0 += 32) drain_chunk<EPI, 32>(c, ldc, M, n_cols, split, row, n0 + c0, t_row + c0, up_col);
+    if (c0 < tile_n) drain_chunk<EPI, 16>(c, ldc, M, n_cols, split, row, n0 + c0, t_row + c0, up_col);
 }
 
 template <int EPI, int AROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
-               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int* __restrict__ status) {
-    constexpr int STAGES = Ring<AROWS>::STAGES, A_BYTES = Ring<AROWS>::A_BYTES, STAGE_BYTES = Ring<AROWS>::STAGE_BYTES;
-    constexpr int RING_BYTES = Ring<AROWS>::RING_BYTES;
+               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status) {
+    constexpr int A_BYTES = Ring<AROWS>::A_BYTES, RING_BYTES = Ring<AROWS>::RING_BYTES, MAX_STAGES = Ring<AROWS>::MAX_STAGES;
+    const int B_HALF = half_rows * BK * 2, STAGE_BYTES = A_BYTES + 2 * B_HALF;
+    const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE_BYTES);
     extern __shared__ unsigned char smem_raw[];
     // ring at a 1024-byte boundary (swizzle atoms), barriers behind it
     const uint32_t ring = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = ring + RING_BYTES;
-    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t full0 = bars, empty0 = bars + 8 * MAX_STAGES, tfull0 = bars + 16 * MAX_STAGES, tempty0 = tfull0 + 16;
     const uint32_t tmem_slot = tempty0 + 16;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_addr(smem_raw)));
 
@@ -139,7 +146,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
     const int n_cols = GATED ? N / 2 : N;                       // columns of the output
-    const int tile_n = GATED ? 128 : BN;                        // output columns per tile
+    const int tile_n = GATED ? half_rows : 2 * half_rows;       // output columns per tile
+    const int UP_COL = half_rows;                               // accumulator column where the second half begins
+    const uint32_t idesc = umma_idesc(BM, 2 * half_rows, false, false);
     const int tiles_m = (M + BM - 1) / BM, tiles_n = (n_cols + tile_n - 1) / tile_n;
     const int tiles_mn = tiles_m * tiles_n, num_tiles = tiles_mn * k_splits;
     const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
@@ -178,7 +187,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t b_dst = ring + i * STAGE_BYTES + A_BYTES, bar = full0 + 8 * i;
                     mbar_expect_tx(bar, STAGE_BYTES);
                     tma_load_2d(b_dst, &map_w, bar, (kb_lo + i) * BK, n0);
-                    tma_load_2d(b_dst + B_HALF_BYTES, &map_w, bar, (kb_lo + i) * BK, GATED ? up_row_offset + n0 : n0 + 128);
+                    tma_load_2d(b_dst + B_HALF, &map_w, bar, (kb_lo + i) * BK, GATED ? up_row_offset + n0 : n0 + half_rows);
                 }
             }
             pdl_wait();
@@ -196,7 +205,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         mbar_expect_tx(bar, STAGE_BYTES);
                         tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
                         tma_load_2d(b_dst, &map_w, bar, kb * BK, n0);
-                        tma_load_2d(b_dst + B_HALF_BYTES, &map_w, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + 128);
+                        tma_load_2d(b_dst + B_HALF, &map_w, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + half_rows);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -227,7 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), IDESC,
+                        tc_mma(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), idesc,
                                (kb > kb_lo || k > 0) ? 1u : 0u);
                     tc_commit(empty0 + 8 * stage);          // the stage is free once these products are done
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -248,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int m0 = (mn % tiles_m) * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
             tc_fence_after();
-            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, split, m0, n0, tmem_base + acc * BN, quarter, lane);
+            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, UP_COL, split, m0, n0, tmem_base + acc * BN, quarter, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty0 + 8 * acc);   // this warp has drained its quarter
@@ -306,6 +315,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
     const int n_cols = GATED ? N / 2 : N;
     const int tile_n = GATED ? 128 : BN;
+    constexpr int UP_COL = 128;
     const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (n_cols + tile_n - 1) / tile_n;
     const int tiles_mn = tiles_m * tiles_n, num_tiles = tiles_mn * k_splits;
     const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
@@ -406,7 +416,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int m0 = (mn % tiles_m) * 2 * BM + (int)rank * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
             tc_fence_after();
-            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, split, m0, n0, tmem_base + acc * BN, quarter, lane);
+            drain_accumulator<EPI>(c, ldc, M, n_cols, tile_n, UP_COL, split, m0, n0, tmem_base + acc * BN, quarter, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -483,7 +493,9 @@ static int tensor_map(const void* ptr, int rows, int cols, int ld, int box_rows,
 
 template <int EPI, int AROWS>
 static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                       int k_splits, int* status, int ctas, cudaStream_t stream) {
+                       int k_splits, int half_rows, int* status, int ctas, cudaStream_t stream) {
+    // the tensor core reads 128 rows at a stage's A address whatever AROWS is: a stage must hold that many bytes
+    if (Ring<AROWS>::A_BYTES + 2 * half_rows * BK * 2 < 128 * BK * 2) return WLLM_BAD_SIZE;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, AROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -492,7 +504,7 @@ static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, in
         configured = true;
     }
     return wllm_launch(gemm_tc_kernel<EPI, AROWS>, ctas, NUM_THREADS, Ring<AROWS>::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
-                       up_off, k_splits, status);
+                       up_off, k_splits, half_rows, status);
 }
 
 // How many pairs can be resident at once.  The kernel is persistent with a fixed stride over the tiles, so
@@ -555,19 +567,21 @@ static int a_rows_for(int M) { return M <= 32 ? 32 : (M <= 64 ? 64 : 128); }
 
 template <int EPI>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                  int k_splits, int* status, int ctas, cudaStream_t stream) {
+                  int k_splits, int half_rows, int* status, int ctas, cudaStream_t stream) {
     switch (a_rows_for(M)) {
-        case 32: return launch_rows<EPI, 32>(ma, mw, c, ldc, M, N, K, up_off, k_splits, status, ctas, stream);
-        case 64: return launch_rows<EPI, 64>(ma, mw, c, ldc, M, N, K, up_off, k_splits, status, ctas, stream);
+        case 32: return launch_rows<EPI, 32>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream);
+        case 64: return launch_rows<EPI, 64>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream);
     }
-    return launch_rows<EPI, 128>(ma, mw, c, ldc, M, N, K, up_off, k_splits, status, ctas, stream);
+    return launch_rows<EPI, 128>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, ctas, stream);
 }
 
 // C = A W^T.  epilogue 0: bf16 C [M, N]; 1: fp32 C [M, N]; 2 / 3: W = [gate; up] ([N, K], N even), bf16 C [M, N/2]
 // = gelu_tanh(gate) * up / silu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
 // k_splits > 1 needs epilogue 1 and a C of k_splits slabs [M, ldc]; every part must hold at least one block of K.
+// half_rows (a multiple of 16 up to 128; 0 = 128) sets the tile of products of at most 128 rows: 2 * half_rows
+// output columns, or half_rows columns of the gated output.
 WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
-                               int epilogue, int k_splits, int* status, int max_ctas, cudaStream_t stream) {
+                               int epilogue, int k_splits, int half_rows, int* status, int max_ctas, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return WLLM_OK;
     if (k_splits < 1 || (k_splits > 1 && epilogue != EPI_F32)) return WLLM_BAD_SIZE;
     {
@@ -578,13 +592,16 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     if (((uintptr_t)a & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15)) return WLLM_BAD_ALIGN;
     const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU;
     if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
+    const bool pair = M > BM && max_ctas >= 2 && pair_enabled();
+    if (half_rows == 0 || pair) half_rows = 128;
+    if (half_rows < 16 || half_rows > 128 || half_rows % 16 != 0) return WLLM_BAD_SIZE;
     CUtensorMap ma, mw;
     int r = tensor_map(a, M, K, lda, a_rows_for(M), &ma);
     if (r) return r;
-    r = tensor_map(w, N, K, ldw, 128, &mw);
+    r = tensor_map(w, N, K, ldw, half_rows, &mw);
     if (r) return r;
-    const int n_cols = gated ? N / 2 : N, tile_n = gated ? 128 : BN;
-    if (M > BM && max_ctas >= 2 && pair_enabled()) {
+    const int n_cols = gated ? N / 2 : N, tile_n = gated ? half_rows : 2 * half_rows;
+    if (pair) {
         const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((n_cols + tile_n - 1) / tile_n) * k_splits;
         const int pairs = tiles < max_ctas / 2 ? tiles : max_ctas / 2;
         switch (epilogue) {
@@ -598,10 +615,10 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     const int tiles = ((M + BM - 1) / BM) * ((n_cols + tile_n - 1) / tile_n) * k_splits;
     const int ctas = tiles < max_ctas ? tiles : max_ctas;
     switch (epilogue) {
-        case EPI_BF16: return launch<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, 1, status, ctas, stream);
-        case EPI_F32: return launch<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, status, ctas, stream);
-        case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, ctas, stream);
-        case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, ctas, stream);
+        case EPI_BF16: return launch<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, 1, half_rows, status, ctas, stream);
+        case EPI_F32: return launch<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, half_rows, status, ctas, stream);
+        case EPI_GATED_GELU: return launch<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
+        case EPI_GATED_SILU: return launch<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, ctas, stream);
     }
     return WLLM_BAD_SIZE;
 }

@@ -137,7 +137,7 @@ static int launch_out(float* resid, const void* delta, int delta_splits, size_t 
     const bool vec = H % 4 == 0 && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)delta & 15) == 0 &&
                      ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0 && delta_split_stride % 4 == 0;
     const int per = vec ? 4 : 1;
-    const int threads = H / per >= 1024 ? 512 : (H / per >= 256 ? 256 : 128);
+    const int threads = H / per >= 512 ? 512 : (H / per >= 256 ? 256 : 128);   // one vector a thread up to 2048 columns
 #define GO(TO, V) wllm_launch(rmsnorm_kernel<TD, TW, TO, V>, n, threads, 0, stream, resid, (const TD*)delta, delta_splits, \
                        delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H)
     if (out_dtype == WLLM_BF16) return vec ? GO(bf16, 4) : GO(bf16, 1);

@@ -53,6 +53,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+template <int W> __device__ __forceinline__ void tc_ld(uint32_t taddr, uint32_t (&r)[W]);
+template <> __device__ __forceinline__ void tc_ld<32>(uint32_t taddr, uint32_t (&r)[32]) { tc_ld32(taddr, r); }
+template <> __device__ __forceinline__ void tc_ld<16>(uint32_t taddr, uint32_t (&r)[16]) { tc_ld16(taddr, r); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups of
@@ -71,7 +81,7 @@ __device__ __forceinline__ uint64_t smem_desc_mn(uint32_t addr, uint32_t mn_bloc
 }
 // Instruction descriptor of kind::f16 with bf16 operands and an fp32 accumulator: bits 4-5 = 1 (fp32 D),
 // 7-9 and 10-12 = 1 (bf16 A, B), bit 15 / 16 = A / B is MN-major, N >> 3 in bits 17-22, M >> 4 in 24-28.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool a_mn_major, bool b_mn_major) {
+__host__ __device__ constexpr __forceinline__ uint32_t umma_idesc(int m, int n, bool a_mn_major, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }

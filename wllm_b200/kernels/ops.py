@@ -12,6 +12,8 @@ graph replays its launches without passing here; the engine adds those itself).
 """
 from __future__ import annotations
 
+import functools
+
 import ctypes
 from ctypes import c_float, c_int, c_void_p
 
@@ -255,20 +257,43 @@ def tc_gemm_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+@functools.lru_cache(maxsize=4096)
+def tile_plan(M: int, N: int, K: int, gated: bool = False, may_split: bool = True) -> tuple:
+    """(half_rows, parts) for a product of at most 128 rows, which is bound by streaming W: the W tile of a
+    stage is two halves of `half_rows` rows, and K is cut into `parts` (at most 16: whoever reads the partial
+    sums loads that many at once).  Chosen so that tiles x parts fill the SMs evenly: the cost of a choice is
+    the bytes of W that the busiest CTA streams, plus a fixed price per tile and a little per part."""
+    if M > 128:
+        return 128, 1
+    least = 48 if M <= 32 else (32 if M <= 64 else 16)     # a stage must hold the 128 rows the tensor core reads at A
+    kblocks = -(-K // 64)
+    cols = N // 2 if gated else N
+    best = None
+    for half in (128, 112, 96, 80, 64, 48, 32, 16):
+        if half < least:
+            continue
+        tiles = -(-cols // (half if gated else 2 * half))
+        wanted = max(1, min(kblocks, SM_COUNT // tiles, 16)) if may_split else 1
+        per = -(-kblocks // wanted)
+        parts = -(-kblocks // per)
+        waves = -(-(tiles * parts) // SM_COUNT)
+        cost = waves * (per * half + 192) * (1.0 + 0.004 * parts)
+        if best is None or cost < best[0]:
+            best = (cost, half, parts)
+    return best[1], best[2]
+
+
 def split_plan(M: int, N: int, K: int) -> int:
     """Parts to cut K into so that a product of few rows still gives every SM a share of the weights."""
-    tiles = -(-M // 128) * -(-N // 256)
-    kblocks = -(-K // 64)
-    wanted = max(1, min(kblocks, SM_COUNT // tiles))
-    per = -(-kblocks // wanted)
-    return -(-kblocks // per)
+    return tile_plan(M, N, K)[1]
 
 
 def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
-                 max_ctas: int = SM_COUNT, k_splits: int = 1) -> torch.Tensor:
+                 max_ctas: int = SM_COUNT, k_splits: int = 1, half_rows: int | None = None) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
     'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
-    k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums."""
+    k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums.
+    half_rows: the tile of products of at most 128 rows (see tile_plan, which chooses it when None)."""
     _need_cuda(a, w, out)
     if not tc_gemm_ok(a, w):
         raise KernelError("gemm_bf16_tc: bfloat16 operands with K and row pitches in steps of 8 elements, 16-byte "
@@ -285,8 +310,10 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     assert k_splits == 1 or (code == 1 and out.is_contiguous())
     status = _status_word(a.device)
     lib = load_family("gemm_bf16_tc")
+    if half_rows is None:
+        half_rows = tile_plan(M, N, K, code >= 2, k_splits > 1)[0]
     _check(lib.wllm_gemm_bf16_tc(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(-2), M, N, K, code,
-                                 k_splits, _ptr(status), max_ctas, _stream()),
+                                 k_splits, half_rows, _ptr(status), max_ctas, _stream()),
            f"gemm_bf16_tc({M}x{N}x{K}, {epilogue}, {k_splits} parts)")
     return out
 
