@@ -448,7 +448,9 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
                  int* __restrict__ arrivals, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_last;
-    pdl_begin();
+    pdl_launch_dependents();
+    // The step's index arrays were copied before its first kernel started, and no kernel of this step writes
+    // a key below the new token's place: they may be read before this kernel waits for its predecessor.
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
@@ -465,12 +467,39 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     const int* table = block_table + (size_t)r * max_pages;
     const int page_shift = 31 - __clz(page_size);
     const int t0 = key_lo / WS_BN, t1 = key_lo >= key_hi ? t0 : (key_hi + WS_BN - 1) / WS_BN;
+    const int box_rows = page_size < WS_BN ? page_size : WS_BN;
+
+    // one tile of keys and values into stage s (the producer lane calls this)
+    auto load_tile = [&](int t, int s) {
+        const uint32_t k_dst = base + (2 * s) * WS_TILE_BYTES, v_dst = k_dst + WS_TILE_BYTES, bar = full0 + 8 * s;
+        mbar_expect_tx(bar, 2 * WS_TILE_BYTES);
+        for (int r0 = 0; r0 < WS_BN; r0 += box_rows) {
+            const int key = t * WS_BN + r0, index = key >> page_shift;
+            int page = index < max_pages ? table[index] : 0;
+            if (page < 0) page = 0;
+            const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+#pragma unroll
+            for (int cb = 0; cb < HD / 64; ++cb) {
+                tma_load_2d(k_dst + cb * (WS_BN * 128) + r0 * 128, &k_map, bar, cb * 64, row);
+                tma_load_2d(v_dst + cb * (WS_BN * 128) + r0 * 128, &v_map, bar, cb * 64, row);
+            }
+        }
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < WS_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    __syncthreads();
+    // Tiles that end below the new token's place hold only keys of earlier steps: the first stages are
+    // requested now, while the kernel that writes the new key and value (and the query) still runs.
+    int early = 0;
+    if (warp == WS_CONSUMERS && lane == 0) {
+        early = max(0, min(WS_STAGES, min(t1, pos / WS_BN) - t0));
+        for (int n = 0; n < early; ++n) load_tile(t0 + n, n);
+    }
+    pdl_wait();
     load_q_tile<WS_THREADS, 16>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
     cp_commit();
     cp_wait<0>();
@@ -482,24 +511,11 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     if (warp == WS_CONSUMERS) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            const int box_rows = page_size < WS_BN ? page_size : WS_BN;
-            int n = 0;
-            for (int t = t0; t < t1; ++t, ++n) {
+            int n = early;
+            for (int t = t0 + early; t < t1; ++t, ++n) {
                 const int s = n % WS_STAGES;
                 if (!mbar_wait(empty0 + 8 * s, ((n / WS_STAGES) & 1) ^ 1)) { ok = false; break; }
-                const uint32_t k_dst = base + (2 * s) * WS_TILE_BYTES, v_dst = k_dst + WS_TILE_BYTES, bar = full0 + 8 * s;
-                mbar_expect_tx(bar, 2 * WS_TILE_BYTES);
-                for (int r0 = 0; r0 < WS_BN; r0 += box_rows) {
-                    const int key = t * WS_BN + r0, index = key >> page_shift;
-                    int page = index < max_pages ? table[index] : 0;
-                    if (page < 0) page = 0;
-                    const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
-#pragma unroll
-                    for (int cb = 0; cb < HD / 64; ++cb) {
-                        tma_load_2d(k_dst + cb * (WS_BN * 128) + r0 * 128, &k_map, bar, cb * 64, row);
-                        tma_load_2d(v_dst + cb * (WS_BN * 128) + r0 * 128, &v_map, bar, cb * 64, row);
-                    }
-                }
+                load_tile(t, s);
             }
             // stay until the consumers have handed back every stage that was filled (a stage that was
             // never filled passes at once), so that nothing is in flight when the CTA leaves

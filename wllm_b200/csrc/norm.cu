@@ -63,24 +63,37 @@ __device__ __forceinline__ void add_parts(float (&v)[4], const TD* __restrict__ 
 }
 
 // VEC = 4: rows whose width is a multiple of 4 are read and written four elements at a time.
-template <typename TD, typename TW, typename TO, int VEC>
+// VPT = 1, 2 or 4: the whole row fits in registers with that many vectors a thread, and memory is passed
+// over once; VPT = 0: wider rows (or VEC = 1) take two passes.
+template <typename TD, typename TW, typename TO, int VEC, int VPT>
 __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, int delta_splits,
                                size_t delta_split_stride, const TW* __restrict__ w, float eps, float offset,
                                TO* __restrict__ out, const int* __restrict__ rows, int H) {
     __shared__ float scratch[32];
-    pdl_begin();
+    pdl_launch_dependents();
+    constexpr bool one_pass = VEC == 4 && VPT > 0;
+    constexpr int NV = VPT > 0 ? VPT : 1;
+    float wv[NV][4];
+    if (one_pass) {          // the gain is written by no kernel: it is read while the predecessor still runs
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = (threadIdx.x + k * blockDim.x) * 4;
+            wv[k][0] = wv[k][1] = wv[k][2] = wv[k][3] = 0.f;
+            if (c < H) load4(w + c, wv[k]);
+        }
+    }
+    pdl_wait();
     const int i = blockIdx.x;
     const int row = rows ? rows[i] : i;
     float* r = resid + (size_t)row * H;
     const TD* d = delta ? delta + (size_t)row * H : nullptr;
     const bool write_back = (d != nullptr) && (rows == nullptr);
     TO* o = out + (size_t)i * H;
-    if (VEC == 4 && H <= (int)blockDim.x * 16) {
-        // the whole row fits in registers (at most four vectors a thread): one pass over memory
-        float v[4][4];
+    if (one_pass) {
+        float v[NV][4];
         float ss = 0.f;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < NV; ++k) {
             const int c = (threadIdx.x + k * blockDim.x) * 4;
             v[k][0] = v[k][1] = v[k][2] = v[k][3] = 0.f;
             if (c < H) {
@@ -93,14 +106,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__
         ss = block_sum(ss, scratch);
         const float inv = 1.0f / sqrtf(ss / (float)H + eps);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
+        for (int k = 0; k < NV; ++k) {
             const int c = (threadIdx.x + k * blockDim.x) * 4;
             if (c < H) {
-                float wv[4], y[4];
-                load4(w + c, wv);
+                float y[4];
                 if (write_back) store4(r + c, v[k]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) y[e] = (v[k][e] * inv) * (offset + wv[e]);
+                for (int e = 0; e < 4; ++e) y[e] = (v[k][e] * inv) * (offset + wv[k][e]);
                 store4(o + c, y);
             }
         }
@@ -138,10 +150,13 @@ static int launch_out(float* resid, const void* delta, int delta_splits, size_t 
                      ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0 && delta_split_stride % 4 == 0;
     const int per = vec ? 4 : 1;
     const int threads = H / per >= 512 ? 512 : (H / per >= 256 ? 256 : 128);   // one vector a thread up to 2048 columns
-#define GO(TO, V) wllm_launch(rmsnorm_kernel<TD, TW, TO, V>, n, threads, 0, stream, resid, (const TD*)delta, delta_splits, \
+    const int vpt = !vec ? 0 : (H <= threads * 4 ? 1 : (H <= threads * 8 ? 2 : (H <= threads * 16 ? 4 : 0)));
+#define GO(TO, V, P) wllm_launch(rmsnorm_kernel<TD, TW, TO, V, P>, n, threads, 0, stream, resid, (const TD*)delta, delta_splits, \
                        delta_split_stride, (const TW*)w, eps, offset, (TO*)out, rows, H)
-    if (out_dtype == WLLM_BF16) return vec ? GO(bf16, 4) : GO(bf16, 1);
-    if (out_dtype == WLLM_F32) return vec ? GO(float, 4) : GO(float, 1);
+#define PICK(TO) (vpt == 1 ? GO(TO, 4, 1) : vpt == 2 ? GO(TO, 4, 2) : vpt == 4 ? GO(TO, 4, 4) : vec ? GO(TO, 4, 0) : GO(TO, 1, 0))
+    if (out_dtype == WLLM_BF16) return PICK(bf16);
+    if (out_dtype == WLLM_F32) return PICK(float);
+#undef PICK
 #undef GO
     return WLLM_BAD_DTYPE;
 }
