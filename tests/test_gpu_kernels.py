@@ -112,6 +112,38 @@ def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(4, 1, 32, 32, 16), (3, 3, 48, 48, 32), (6, 2, 80, 40, 16), (2, 2, 64, 32, 16),
+                                              (8, 1, 256, 256, 64)])
+def test_rope_kv_write_of_many_tokens_is_the_same_arithmetic(dtype, nq, nkv, hd, rot, ps):
+    """From 256 tokens on one CTA walks all heads of a token (16-byte accesses where the sizes allow): the
+    reference, and bit for bit what the launch for few tokens writes."""
+    g = torch.Generator().manual_seed(5)
+    n = 300
+    pages = -(-n // ps) + 2
+    qkv = torch.randn(n, (nq + 2 * nkv) * hd, generator=g).to(dtype)
+    positions = torch.randint(0, 8000, (n,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * ps, generator=g)[:n].to(torch.int32)
+    slots[7] = -1
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    k_ref = torch.zeros(pages, nkv, ps, hd, dtype=dtype)
+    v_ref, q_ref = torch.zeros_like(k_ref), torch.zeros(n, nq * hd, dtype=dtype)
+    ref.rope_kv_write(qkv, q_ref, positions, slots, inv_freq, k_ref, v_ref, nq, nkv, hd, rot, ps)
+    many = [torch.zeros_like(t, device=DEV) for t in (q_ref, k_ref, v_ref)]
+    ops().rope_kv_write(qkv.to(DEV), many[0], positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), many[1], many[2], nq, nkv, hd,
+                        rot, ps)
+    t = dict(rtol=1e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+    torch.testing.assert_close(many[0].cpu().float(), q_ref.float(), **t)
+    torch.testing.assert_close(many[1].cpu().float(), k_ref.float(), **t)
+    assert torch.equal(many[2].cpu(), v_ref)
+    few = [torch.zeros_like(t, device=DEV) for t in (q_ref, k_ref, v_ref)]
+    for lo in range(0, n, 100):            # the same rows, a hundred at a time
+        ops().rope_kv_write(qkv[lo:lo + 100].to(DEV), few[0][lo:lo + 100], positions[lo:lo + 100].to(DEV),
+                            slots[lo:lo + 100].to(DEV), inv_freq.to(DEV), few[1], few[2], nq, nkv, hd, rot, ps)
+    for a, b in zip(many, few):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rmsnorm_adds_partial_sums_in_order(dtype):
     g = torch.Generator().manual_seed(8)
     n, H = 6, 2048
