@@ -778,25 +778,33 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
 // --------------------------------------------------------------------------------------
 // prefill on the fifth-generation tensor cores (head sizes in steps of 64): grid as above
 // --------------------------------------------------------------------------------------
-// 128 query rows per CTA are the 128 lanes of tensor memory.  Roles by warp:
-//   warp 0      one lane issues the TMA box copies of the key tiles and the value tiles (64 keys each,
-//               two stages each, keys and values on barriers of their own: a key stage is free as soon as
-//               its scores are computed, a value stage once it has been accumulated);
-//   warp 1      one lane issues tcgen05.mma: scores S = Q K^T (M 128, N 64, K = head size) into one of two
-//               score buffers in tensor memory, one tile ahead of the softmax, and O += P V (M 128,
-//               N = head size, K 64) with P from shared memory and V as an MN-major operand straight
-//               from the value tile (no transpose);
-//   warps 2-5   one thread per row: read the row's 64 scores with tcgen05.ld, mask, scale, running maximum
-//               and sum in registers without a shuffle, write P as bfloat16 into shared memory in the
-//               layout the tensor core reads, and rescale the row of O in tensor memory only when some
-//               row of the warp has a new maximum.  At the end they normalise O and store it.
+// 128 query rows per CTA are the 128 lanes of tensor memory.  Shared memory holds nothing but key and value
+// tiles: the kernel is bound by shared-memory bandwidth when the tensor core has to read Q (for the scores)
+// and P (for the output) from there beside K and V, so both A operands live in tensor memory instead.
+// Columns: O [0, head size), two score buffers of 64 at 256 and 320, Q (two elements a column) from 384.
+// Roles by warp:
+//   warps 0, 6  one lane of warp 0 issues the TMA box copies of the key tiles, one lane of warp 6 those of
+//               the value tiles (64 keys each, three stages each, on barriers of their own: a key stage is
+//               free as soon as its scores are computed, a value stage once it has been accumulated);
+//   warp 1      one lane issues tcgen05.mma: scores S = Q K^T (M 128, N 64, K = head size; Q from tensor
+//               memory) into one of two score buffers, one tile ahead of the softmax, and O += P V (M 128,
+//               N = head size, K 64) with P from tensor memory and V as an MN-major operand straight from
+//               the value tile (no transpose);
+//   warps 2-5   one thread per row: store the row of Q into tensor memory once; then per tile read the
+//               row's 64 scores with tcgen05.ld, mask, scale, running maximum and sum in registers without
+//               a shuffle, write P as bfloat16 over the scores it has just read, and rescale the row of O
+//               only when some row of the warp has a new maximum.  At the end they normalise O and store it.
+// The tensor core runs its instructions in the order of issue: S(n + 2) is issued after P V(n), which reads
+// the P that lies in S(n + 2)'s buffer, so the buffers need no barrier of their own.
 // All waits are bounded; a role that gives up records a code and every role leaves through the common
 // exit, where tensor memory is freed.
-constexpr int TC_BM = 128, TC_BN = 64, TC_KV_STAGES = 2;
-constexpr int TC_Q_BYTES = TC_BM * ROWB, TC_KV_BYTES = TC_BN * ROWB, TC_P_BYTES = TC_BM * 128;
-constexpr int TC_SMEM = 1024 + TC_Q_BYTES + 2 * TC_KV_STAGES * TC_KV_BYTES + TC_P_BYTES + 256;
-constexpr int TC_THREADS = 192;
+constexpr int TC_BM = 128, TC_BN = 64, TC_KV_STAGES = 3;
+constexpr int TC_KV_BYTES = TC_BN * ROWB;
+constexpr int TC_SMEM = 1024 + 2 * TC_KV_STAGES * TC_KV_BYTES + 256;
+constexpr int TC_THREADS = 224;
 constexpr int TC_S_COL = 256;                      // score buffers behind the output accumulator
+constexpr int TC_Q_COL = 384;                      // the query tile: HD / 2 columns
+constexpr float TC_MAX_SLACK = 8.0f;
 constexpr uint32_t IDESC_S = umma_idesc(TC_BM, TC_BN, false, false);
 constexpr uint32_t IDESC_PV = umma_idesc(TC_BM, HD, false, true);       // V is MN-major
 enum { GAVE_UP_TC_LOAD = 23, GAVE_UP_TC_MMA = 24, GAVE_UP_TC_SOFTMAX = 25 };
@@ -825,10 +833,10 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_s = base, k_s = q_s + TC_Q_BYTES, v_s = k_s + TC_KV_STAGES * TC_KV_BYTES;
-    const uint32_t p_s = v_s + TC_KV_STAGES * TC_KV_BYTES, bars = p_s + TC_P_BYTES;
-    const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, v_full = bars + 40, v_empty = bars + 56;
-    const uint32_t s_full = bars + 72, s_empty = bars + 88, p_full = bars + 104, pv_done = bars + 112, tmem_slot = bars + 120;
+    const uint32_t k_s = base, v_s = k_s + TC_KV_STAGES * TC_KV_BYTES, bars = v_s + TC_KV_STAGES * TC_KV_BYTES;
+    const uint32_t k_full = bars, k_empty = k_full + 8 * TC_KV_STAGES, v_full = k_empty + 8 * TC_KV_STAGES;
+    const uint32_t v_empty = v_full + 8 * TC_KV_STAGES, s_full = v_empty + 8 * TC_KV_STAGES;
+    const uint32_t q_full = s_full + 16, p_full = q_full + 8, pv_done = p_full + 8, tmem_slot = pv_done + 8;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int last_row = min(rows, row0 + TC_BM) - 1;
@@ -839,12 +847,12 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const int* table = block_table + (size_t)r * max_pages;
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 4);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < TC_KV_STAGES; ++s) {
             mbar_init(k_full + 8 * s, 1); mbar_init(k_empty + 8 * s, 1);
             mbar_init(v_full + 8 * s, 1); mbar_init(v_empty + 8 * s, 1);
-            mbar_init(s_full + 8 * s, 1); mbar_init(s_empty + 8 * s, 4);
         }
+        mbar_init(s_full, 1); mbar_init(s_full + 8, 1);
+        mbar_init(q_full, 4);
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -856,33 +864,36 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
+    if (warp == 0 || warp == 6) {
+        // ---------------- TMA producers: warp 0 the key tiles, warp 6 the value tiles ----------------
+        // (one thread for both would hold back the next key tile while it waits for a value stage, which
+        // is handed back a tile later than the key stage of the same tile)
         if (lane == 0) {
+            const int kv = warp == 6;
+            const uint32_t full0 = kv ? v_full : k_full, empty0 = kv ? v_empty : k_empty, ring = kv ? v_s : k_s;
+            const CUtensorMap* map = kv ? &v_map : &k_map;
             const int box_rows = page_size < TC_BN ? page_size : TC_BN;
             bool ok = true;
             int n = 0;
             for (; n < T && ok; ++n) {
-                const int s = n & 1, ph = (n >> 1) & 1, tile_start = (t0 + n) * TC_BN;
-                for (int kv = 0; kv < 2 && ok; ++kv) {
-                    if (!mbar_wait((kv ? v_empty : k_empty) + 8 * s, ph ^ 1)) { ok = false; break; }
-                    const uint32_t bar = (kv ? v_full : k_full) + 8 * s, dst = (kv ? v_s : k_s) + s * TC_KV_BYTES;
-                    mbar_expect_tx(bar, TC_KV_BYTES);
-                    for (int r0 = 0; r0 < TC_BN; r0 += box_rows) {
-                        const int key = tile_start + r0, index = key >> page_shift;
-                        int page = index < max_pages ? table[index] : 0;
-                        if (page < 0) page = 0;
-                        const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+                const int s = n % TC_KV_STAGES, ph = (n / TC_KV_STAGES) & 1, tile_start = (t0 + n) * TC_BN;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
+                const uint32_t bar = full0 + 8 * s, dst = ring + s * TC_KV_BYTES;
+                mbar_expect_tx(bar, TC_KV_BYTES);
+                for (int r0 = 0; r0 < TC_BN; r0 += box_rows) {
+                    const int key = tile_start + r0, index = key >> page_shift;
+                    int page = index < max_pages ? table[index] : 0;
+                    if (page < 0) page = 0;
+                    const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
 #pragma unroll
-                        for (int cb = 0; cb < HD / 64; ++cb)
-                            tma_load_2d(dst + cb * (TC_BN * 128) + r0 * 128, kv ? &v_map : &k_map, bar, cb * 64, row);
-                    }
+                    for (int cb = 0; cb < HD / 64; ++cb)
+                        tma_load_2d(dst + cb * (TC_BN * 128) + r0 * 128, map, bar, cb * 64, row);
                 }
             }
             // stay until the stages that were filled have been handed back: nothing in flight at the exit
-            for (int k = 0; k < 2 && ok; ++k, ++n) {
-                const int s = n & 1, ph = (n >> 1) & 1;
-                if (!mbar_wait(k_empty + 8 * s, ph ^ 1) || !mbar_wait(v_empty + 8 * s, ph ^ 1)) ok = false;
+            for (int k = 0; k < TC_KV_STAGES && ok; ++k, ++n) {
+                const int s = n % TC_KV_STAGES, ph = (n / TC_KV_STAGES) & 1;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) ok = false;
             }
             if (!ok) atomicExch(status, GAVE_UP_TC_LOAD);
         }
@@ -890,30 +901,31 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             bool ok = mbar_wait(q_full, 0);
+            tc_fence_after();
             auto issue_scores = [&](int n) -> bool {       // S(n) = Q K(n)^T into score buffer n % 2
-                const int s = n & 1, ph = (n >> 1) & 1;
-                if (!mbar_wait(k_full + 8 * s, ph) || !mbar_wait(s_empty + 8 * s, ph ^ 1)) return false;
+                const int s = n % TC_KV_STAGES, ph = (n / TC_KV_STAGES) & 1;
+                if (!mbar_wait(k_full + 8 * s, ph)) return false;
                 tc_fence_after();
-                const uint32_t d = tmem_base + TC_S_COL + s * TC_BN, kb = k_s + s * TC_KV_BYTES;
+                const uint32_t d = tmem_base + TC_S_COL + (n & 1) * TC_BN, kb = k_s + s * TC_KV_BYTES;
 #pragma unroll
                 for (int kt = 0; kt < HD / 16; ++kt)
-                    tc_mma(d, smem_desc(q_s + (kt >> 2) * (TC_BM * 128) + (kt & 3) * 32),
-                           smem_desc(kb + (kt >> 2) * (TC_BN * 128) + (kt & 3) * 32), IDESC_S, kt > 0 ? 1u : 0u);
+                    tc_mma_ts(d, tmem_base + TC_Q_COL + kt * 8, smem_desc(kb + (kt >> 2) * (TC_BN * 128) + (kt & 3) * 32),
+                              IDESC_S, kt > 0 ? 1u : 0u);
                 tc_commit(k_empty + 8 * s);
-                tc_commit(s_full + 8 * s);
+                tc_commit(s_full + 8 * (n & 1));
                 return true;
             };
             ok = ok && issue_scores(0);
             for (int n = 0; n < T && ok; ++n) {
                 if (n + 1 < T && !issue_scores(n + 1)) { ok = false; break; }
-                const int s = n & 1, ph = (n >> 1) & 1;
+                const int s = n % TC_KV_STAGES, ph = (n / TC_KV_STAGES) & 1;
                 if (!mbar_wait(v_full + 8 * s, ph) || !mbar_wait(p_full, n & 1)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t vb = v_s + s * TC_KV_BYTES;
+                const uint32_t vb = v_s + s * TC_KV_BYTES, pa = tmem_base + TC_S_COL + (n & 1) * TC_BN;
 #pragma unroll
                 for (int kk = 0; kk < TC_BN / 16; ++kk)
-                    tc_mma(tmem_base, smem_desc(p_s + kk * 32), smem_desc_mn(vb + kk * (16 * 128), TC_BN * 128), IDESC_PV,
-                           (n > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem_base, pa + kk * 8, smem_desc_mn(vb + kk * (16 * 128), TC_BN * 128), IDESC_PV,
+                              (n > 0 || kk > 0) ? 1u : 0u);
                 tc_commit(v_empty + 8 * s);
                 tc_commit(pv_done);
             }
@@ -922,23 +934,29 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     } else {
         // ---------------- softmax: one thread per row ----------------
         const int quarter = warp & 3, row = quarter * 32 + lane, m_row = row0 + row;
-        const int epi_tid = threadIdx.x - 64;
-        // the query tile, in the layout the tensor core reads (the same swizzle as a box copy)
-        for (int idx = epi_tid; idx < TC_BM * CPR; idx += 128) {
-            const int rr = idx / CPR, chunk = idx % CPR, m = row0 + rr;
-            const bool valid = m < rows;
-            const bf16* src = valid ? q + (size_t)(q_start + m / rep) * q_stride + (size_t)(g * rep + m % rep) * HD + chunk * 8 : q;
-            cp_async16(q_s + swz<TC_BM>(rr, chunk), src, valid);
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // the row of Q into tensor memory: element pairs (k, k + 1) share a column
+        {
+            const bf16* src = m_row < rows ? q + (size_t)(q_start + m_row / rep) * q_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+                uint32_t w[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (src) v = *reinterpret_cast<const uint4*>(src + 2 * c0 + 8 * j);
+                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+                }
+                tc_st32(t_lane + TC_Q_COL + c0, w);
+            }
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_full);
         }
-        cp_commit();
-        cp_wait<0>();
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(q_full);
 
         const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
         const int first_row = window > 0 ? max(0, pos_row - window + 1) : 0;
-        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int n = 0; n < T; ++n) {
@@ -949,43 +967,50 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             tc_ld32(t_lane + TC_S_COL + b * TC_BN, sv[0]);
             tc_ld32(t_lane + TC_S_COL + b * TC_BN + 32, sv[1]);
             tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty + 8 * b);          // the score buffer may be overwritten
             // Scores stay unscaled until the exponent: max(scale * s) = scale * max(s) for scale > 0, and
             // exp2(scale * s - scale * m) is one fused multiply-add and one ex2 per element.  Only tiles at the
             // causal edge or the window's start need the per-key mask; the warp decides together.
             const bool inner = __all_sync(0xffffffffu, key0 + TC_BN - 1 <= pos_row && key0 >= first_row);
-            float mx = -INFINITY;
+            // One warp runs alone on its scheduler, so a chain of dependent maxima or additions would cost its
+            // full latency per element: four independent chains each (the order is fixed all the same).
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (inner) {
 #pragma unroll
-                for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c >> 5][c & 31]));
+                for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c >> 5][c & 31]));
             } else {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int key = key0 + c;
                     const float v = (key <= pos_row && key >= first_row) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
                     sv[c >> 5][c & 31] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], v);
                 }
             }
-            const float m_new = fmaxf(m_run, mx * scale2);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // The reference point of the exponents follows the running maximum lazily: it moves only when the
+            // maximum has grown by more than TC_MAX_SLACK (in units of log2), so the probabilities stay below
+            // 2^slack and the row of O has to be rescaled in few tiles instead of in most.  The quotient O / l
+            // does not depend on the reference point.
+            const float m_tile = fmaxf(m_run, mx * scale2);
+            const float m_new = m_tile > m_run + TC_MAX_SLACK ? m_tile : m_run;      // m_run = -inf: takes m_tile
             const float mbase = m_new == -INFINITY ? 0.f : m_new;
             const float corr = fast_exp2(m_run - mbase);
-            float sum = 0.f;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t packed[32];
 #pragma unroll
             for (int c = 0; c < 64; c += 2) {
                 const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, -mbase));
                 const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), scale2, -mbase));
-                sum += p0 + p1;
+                sum4[(c >> 1) & 3] += p0 + p1;
                 packed[c >> 1] = pack_bf16(p0, p1);
             }
-            l_run = l_run * corr + sum;
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             const bool changed = m_new > m_run;
             m_run = m_new;
+            // P over the scores this thread has just read: keys (2j, 2j + 1) in column j of the buffer
+            tc_st32(t_lane + TC_S_COL + b * TC_BN, packed);
             if (n > 0) {
-                if (!mbar_wait(pv_done, (n - 1) & 1)) { ok = false; break; }     // P and O of the tile before are done with
+                if (!mbar_wait(pv_done, (n - 1) & 1)) { ok = false; break; }     // O of the tile before is complete
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, changed)) {
 #pragma unroll 1
@@ -997,17 +1022,9 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                         for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * corr);
                         tc_st32(t_lane + c0, ov);
                     }
-                    tc_wait_st();
                 }
             }
-            // P row: 64 bfloat16 = eight 16-byte chunks, swizzled like a box copy
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const uint32_t addr = p_s + row * 128 + ((j ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * j]), "r"(packed[4 * j + 1]),
-                             "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3]) : "memory");
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
