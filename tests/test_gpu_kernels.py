@@ -276,6 +276,7 @@ MMA_CASES = ATTN_CASES + [
 @pytest.mark.parametrize("window", [0, 24])
 @pytest.mark.parametrize("split_keys", [64, 256])
 def test_attention_mma_decode_and_prefill_cover_a_mixed_batch(case, window, split_keys):
+    """split_keys 64 also lets two prefill CTAs share every tile that walks more than two key tiles."""
     nq, nkv, hd, ps, ctx_lens, q_lens = case
     q, kp, vp, treq, pos, table, (starts, qlens, ctxs) = _mma_inputs(case, seed=11, spike=(window == 0))
     scale = 1.0 / math.sqrt(hd)
@@ -292,8 +293,17 @@ def test_attention_mma_decode_and_prefill_cover_a_mixed_batch(case, window, spli
         o.attention_mma_decode(qd, got, kd, vd, starts, qlens, ctxs, td, nq, nkv, hd, ps, window, scale, split_keys,
                                max_splits, scratch)
     if any(n > 1 for n in q_lens) or not decode:
+        share = 2 if (hd % 64 == 0 and split_keys == 64) else 0
+        halves = torch.full((o.attention_prefill_halves_floats(R, max(q_lens), nq, nkv, hd),), float("nan"), device=DEV) \
+            if share else None
         o.attention_mma_prefill(qd, got, kd, vd, starts, qlens, ctxs, td, max(q_lens), nq, nkv, hd, ps, window, scale,
-                                skip_single=decode)
+                                skip_single=decode, split_above=share, halves=halves)
+        if share:       # whichever of the two CTAs merges, the result is the same
+            again = torch.full_like(got, float("nan"))
+            o.attention_mma_prefill(qd, again, kd, vd, starts, qlens, ctxs, td, max(q_lens), nq, nkv, hd, ps, window,
+                                    scale, skip_single=decode, split_above=share, halves=halves)
+            rows = torch.cat([torch.arange(s, s + n) for s, n in zip(starts.tolist(), q_lens) if n > 1 or not decode])
+            assert torch.equal(again[rows.to(DEV)], got[rows.to(DEV)])
     torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2)
 
 

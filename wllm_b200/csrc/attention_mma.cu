@@ -820,14 +820,20 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                   const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                   const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                   const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
-                  int skip_single, int* __restrict__ status) {
+                  int skip_single, int split_above, float* __restrict__ halves, int* __restrict__ arrivals,
+                  int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
+    __shared__ int s_second;
     pdl_begin();
     const int g = blockIdx.y, r = blockIdx.z;
     const int q_len = req_q_len[r];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
     const int rep = nq / nkv, rows = q_len * rep;
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    // With split_above > 0 the grid holds two CTAs a tile; a tile that walks more than split_above key tiles
+    // is shared between them (each takes half of its keys), the second CTA of any other tile leaves at once.
+    const int parts = split_above > 0 ? 2 : 1;
+    const int slot_x = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int tile = slot_x / parts, part = slot_x % parts;
     const int row0 = tile * TC_BM;
     if (row0 >= rows) return;
     const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
@@ -842,7 +848,14 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const int last_row = min(rows, row0 + TC_BM) - 1;
     const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + row0 / rep;
     const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
-    const int t0 = key_lo / TC_BN, t1 = (key_hi + TC_BN - 1) / TC_BN, T = t1 - t0;
+    int t0 = key_lo / TC_BN, t1 = (key_hi + TC_BN - 1) / TC_BN, T = t1 - t0;
+    const bool shared_tile = split_above > 0 && T > split_above;
+    if (!shared_tile && part == 1) return;
+    if (shared_tile) {          // both halves hold keys of every row: a tile spans at most two key tiles of positions
+        const int mid = t0 + (T + 1) / 2;
+        if (part == 0) t1 = mid; else t0 = mid;
+        T = t1 - t0;
+    }
     const int page_shift = 31 - __clz(page_size);
     const int* table = block_table + (size_t)r * max_pages;
 
@@ -938,16 +951,19 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         // the row of Q into tensor memory: element pairs (k, k + 1) share a column
         {
             const bf16* src = m_row < rows ? q + (size_t)(q_start + m_row / rep) * q_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
+            constexpr int QC = (HD / 2) % 64 == 0 ? 64 : 32;       // columns a round: sixteen (or eight) loads in flight
 #pragma unroll 1
-            for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-                uint32_t w[32];
+            for (int c0 = 0; c0 < HD / 2; c0 += QC) {
+                uint32_t w[QC / 32][32];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < QC / 4; ++j) {
                     uint4 v = make_uint4(0u, 0u, 0u, 0u);
                     if (src) v = *reinterpret_cast<const uint4*>(src + 2 * c0 + 8 * j);
-                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+                    w[j / 8][4 * (j % 8)] = v.x; w[j / 8][4 * (j % 8) + 1] = v.y;
+                    w[j / 8][4 * (j % 8) + 2] = v.z; w[j / 8][4 * (j % 8) + 3] = v.w;
                 }
-                tc_st32(t_lane + TC_Q_COL + c0, w);
+#pragma unroll
+                for (int h = 0; h < QC / 32; ++h) tc_st32(t_lane + TC_Q_COL + c0 + 32 * h, w[h]);
             }
             tc_wait_st();
             tc_fence_before();
@@ -1030,10 +1046,73 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             if (lane == 0) mbar_arrive(p_full);
         }
         if (ok && !mbar_wait(pv_done, (T - 1) & 1)) ok = false;
-        if (ok) {
+        ok = __all_sync(0xffffffffu, ok);        // the tensor-memory loads below are collective: all lanes or none
+        bf16* dst = m_row < rows ? out + (size_t)(q_start + m_row / rep) * out_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
+        if (shared_tile) {
+            // Two CTAs hold halves of this tile's keys.  Each writes its half result (unnormalised O, reference
+            // maximum, sum) and counts itself in; the one that comes second adds the other's to its own, which
+            // is still in tensor memory.  Products and sums are written so that the result does not depend
+            // on which of the two that is (a * fa + b * fb with separate roundings is symmetric).
+            // (every softmax thread passes the two block barriers below, whatever its own waits came to)
+            // Every lane of a warp takes part in the loads, rows past the end too; only their stores are left out.
+            tc_fence_after();
+            const int item = (r * nkv + g) * ((int)gridDim.x / 2) + tile;
+            // a half result: [column chunk of 32][row][32] (a warp writes whole lines), then (maximum, sum) by row
+            float* mine = halves + (size_t)(item * 2 + part) * TC_BM * (HD + 4);
+            const float* other = halves + (size_t)(item * 2 + (part ^ 1)) * TC_BM * (HD + 4);
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD && ok; c0 += 32) {
+                uint32_t ov[32];
+                tc_ld32(t_lane + c0, ov);
+                tc_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    *reinterpret_cast<float4*>(mine + ((size_t)c0 * TC_BM + row * 32) + c) = make_float4(__uint_as_float(ov[c]), __uint_as_float(ov[c + 1]),
+                                                                            __uint_as_float(ov[c + 2]), __uint_as_float(ov[c + 3]));
+            }
+            mine[(size_t)HD * TC_BM + row * 2] = m_run;
+            mine[(size_t)HD * TC_BM + row * 2 + 1] = l_run;
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (row == 0) {
+                const int before = atomicAdd(&arrivals[item], 1);
+                s_second = before;
+                if (before == 1) arrivals[item] = 0;            // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (s_second == 1 && ok) {
+                __threadfence();
+                const float m_b = __ldcg(other + (size_t)HD * TC_BM + row * 2), l_b = __ldcg(other + (size_t)HD * TC_BM + row * 2 + 1);
+                const float M = fmaxf(m_run, m_b), mb = M == -INFINITY ? 0.f : M;
+                const float fa = exp2f(m_run - mb), fb = exp2f(m_b - mb);
+                const float inv = 1.0f / __fadd_rn(__fmul_rn(l_run, fa), __fmul_rn(l_b, fb));
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t ov[32];
+                    tc_ld32(t_lane + c0, ov);
+                    tc_wait_ld();
+                    float y[32];
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 b = __ldcg(reinterpret_cast<const float4*>(other + ((size_t)c0 * TC_BM + row * 32) + c));
+                        y[c] = __fadd_rn(__fmul_rn(__uint_as_float(ov[c]), fa), __fmul_rn(b.x, fb)) * inv;
+                        y[c + 1] = __fadd_rn(__fmul_rn(__uint_as_float(ov[c + 1]), fa), __fmul_rn(b.y, fb)) * inv;
+                        y[c + 2] = __fadd_rn(__fmul_rn(__uint_as_float(ov[c + 2]), fa), __fmul_rn(b.z, fb)) * inv;
+                        y[c + 3] = __fadd_rn(__fmul_rn(__uint_as_float(ov[c + 3]), fa), __fmul_rn(b.w, fb)) * inv;
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 o;
+                        o.x = pack_bf16(y[c], y[c + 1]); o.y = pack_bf16(y[c + 2], y[c + 3]);
+                        o.z = pack_bf16(y[c + 4], y[c + 5]); o.w = pack_bf16(y[c + 6], y[c + 7]);
+                        if (dst) *reinterpret_cast<uint4*>(dst + c0 + c) = o;
+                    }
+                }
+            }
+            if (!ok && lane == 0) atomicExch(status, GAVE_UP_TC_SOFTMAX);
+        } else if (ok) {
             tc_fence_after();
             const float inv = 1.0f / l_run;
-            bf16* dst = m_row < rows ? out + (size_t)(q_start + m_row / rep) * out_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t ov[32];
@@ -1123,16 +1202,25 @@ WLLM_API int wllm_attention_mma_head_dim() { return HD; }
 constexpr int ARRIVAL_SLOTS = 1 << 16;
 constexpr int FUSED_MERGE_SPLITS = 32;     // more splits than this are merged by the second kernel, on many SMs
 static __device__ int g_arrivals[ARRIVAL_SLOTS];
-static int* arrivals_address() {
-    static int* addr[64];
+static __device__ int g_tile_arrivals[ARRIVAL_SLOTS];      // the same for the tiles that two prefill CTAs share
+template <typename Symbol>
+static int* symbol_address(const Symbol& symbol, int** cache) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (addr[dev] == nullptr) {
+    if (cache[dev] == nullptr) {
         void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_arrivals) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-        addr[dev] = static_cast<int*>(p);
+        if (cudaGetSymbolAddress(&p, symbol) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        cache[dev] = static_cast<int*>(p);
     }
-    return addr[dev];
+    return cache[dev];
+}
+static int* arrivals_address() {
+    static int* addr[64];
+    return symbol_address(g_arrivals, addr);
+}
+static int* tile_arrivals_address() {
+    static int* addr[64];
+    return symbol_address(g_tile_arrivals, addr);
 }
 
 // Floats of scratch the decode path needs for `requests` requests: partial outputs and (max, sum) pairs.
@@ -1203,12 +1291,21 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
                        (const float*)part_o, (const float*)part_ml);
 }
 
+// Floats of `halves` for a prefill launch that shares tiles between two CTAs.
+WLLM_API long long wllm_attention_mma_prefill_halves_floats(int requests, int max_q_len, int nq, int nkv) {
+    const long long tiles = ((long long)max_q_len * (nq / nkv) + 127) / 128;
+    return tiles * nkv * requests * 2 * 128 * (HD + 4);
+}
+
 // Tokens of requests with q_len > 1 (and of those with q_len == 1 too unless skip_single).
 WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                         const void* v_pages, long long pool_pages, const int* req_q_start,
                                         const int* req_q_len, const int* req_ctx_len, const int* block_table,
                                         int max_pages, int requests, int max_q_len, int nq, int nkv, int page_size,
-                                        int window, float scale, int skip_single, int* status, cudaStream_t stream) {
+                                        int window, float scale, int skip_single, int split_above, float* halves,
+                                        int* status, cudaStream_t stream) {
+    // split_above > 0 (tensor-memory kernel only): a tile of 128 rows that walks more than split_above tiles of
+    // 64 keys is shared by two CTAs; `halves` then holds wllm_attention_mma_prefill_halves_floats(...) floats.
     if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
     const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
@@ -1235,10 +1332,18 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
 #if (HEAD_DIM % 64 == 0)
-    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0))
-        return wllm_launch(prefill_tc_kernel, dim3(tiles, nkv, requests), TC_THREADS, TC_SMEM, stream,
+    if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+        int* arrivals = nullptr;
+        if (split_above > 0) {
+            if (halves == nullptr || ((uintptr_t)halves & 15) || (long long)tiles * nkv * requests > ARRIVAL_SLOTS) return WLLM_BAD_SIZE;
+            arrivals = tile_arrivals_address();
+            if (arrivals == nullptr) split_above = 0;
+        }
+        return wllm_launch(prefill_tc_kernel, dim3(split_above > 0 ? 2 * tiles : tiles, nkv, requests), TC_THREADS, TC_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
-                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
+                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, split_above, halves,
+                           arrivals, status);
+    }
 #endif
     return wllm_launch(prefill_kernel, dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream,
                        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,

@@ -84,8 +84,20 @@ class StepContext:
             ops.attention_mma_decode(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,
                                      table, nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch)
         if self.num_multi > 0 or not decode:
+            split_above, halves = self._shared_tiles(nq, nkv, hd, skip_single=decode)
             ops.attention_mma_prefill(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,
-                                      table, self.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode)
+                                      table, self.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode,
+                                      split_above=split_above, halves=halves)
+
+    def _shared_tiles(self, nq: int, nkv: int, hd: int, skip_single: bool):
+        """Whether this step's prefill attention shares its heavy tiles between two CTAs (ops.prefill_share_plan),
+        and the buffer for their partial results."""
+        split_above = ops.prefill_share_plan(self.host["req_q_len"].tolist(), self.host["req_ctx_len"].tolist(), nq, nkv,
+                                             hd, skip_single)
+        if split_above <= 0:
+            return 0, None
+        floats = ops.attention_prefill_halves_floats(self.n_requests, self.max_q_len, nq, nkv, hd)
+        return split_above, self.buffer("attention_halves", (floats,), torch.float32)
 
 
 class ModelRunner:

@@ -105,8 +105,12 @@ def attention(args, decode: bool) -> None:
             ops.attention_mma_decode(q, out, k, v, starts, qlens, ctxs, table, nq, nkv, hd, ps, 0, scale, split_keys,
                                      max_splits, scratch)
     else:
+        split_above = 0 if args.no_share else ops.prefill_share_plan([q_len] * R, [ctx] * R, nq, nkv, hd, False)
+        halves = torch.empty(ops.attention_prefill_halves_floats(R, q_len, nq, nkv, hd), device=DEV) if split_above else None
+
         def run():
-            ops.attention_mma_prefill(q, out, k, v, starts, qlens, ctxs, table, q_len, nq, nkv, hd, ps, 0, scale, False)
+            ops.attention_mma_prefill(q, out, k, v, starts, qlens, ctxs, table, q_len, nq, nkv, hd, ps, 0, scale, False,
+                                      split_above=split_above, halves=halves)
     ms = timed(run, args.iters)
     hbm, tf, src = peaks()
     kv_bytes = 2.0 * R * ctx * nkv * hd * 2
@@ -137,6 +141,7 @@ def main(argv=None) -> int:
         a.add_argument("--kv-heads", type=int, default=1)
         a.add_argument("--head-dim", type=int, default=256)
         a.add_argument("--page-size", type=int, default=64)
+        a.add_argument("--no-share", action="store_true", help="prefill: never share a heavy tile between two CTAs")
     for p in sub.choices.values():
         p.add_argument("--iters", type=int, default=10)
     args = ap.parse_args(argv)

@@ -198,11 +198,46 @@ def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_c
     launches += 1 if max_splits > 1 and (hd % 64 != 0 or max_splits > 32) else 0    # the merge kernel, where it is not fused
 
 
+def attention_prefill_halves_floats(requests: int, max_q_len: int, nq: int, nkv: int, hd: int) -> int:
+    """Floats of the `halves` buffer of a prefill launch that shares heavy tiles between two CTAs."""
+    tiles = -(-(max_q_len * (nq // nkv)) // 128)
+    return tiles * nkv * requests * 2 * 128 * (hd + 4)
+
+
+def prefill_share_plan(q_lens, ctx_lens, nq: int, nkv: int, hd: int, skip_single: bool) -> int:
+    """`split_above` for attention_mma_prefill, from the step's request lengths on the host.  A prompt processed
+    from its start gives its 128-row tiles 1, 2, ... tiles of keys to walk, and a grid of at most one CTA an
+    SM then ends with its heaviest tile.  Such a grid is launched with two CTAs a tile, and the tiles that are
+    heavier than a fair share (a quarter above the mean per SM, at least 8) are halved.  0: no sharing."""
+    if hd % 64 != 0:
+        return 0
+    rep = nq // nkv
+    longest = max((n for n in q_lens if not (skip_single and n == 1)), default=0)
+    if longest <= 0 or -(-(longest * rep) // 128) * nkv * len(q_lens) > SM_COUNT:
+        return 0
+    work = heaviest = 0
+    for q_len, ctx_len in zip(q_lens, ctx_lens):
+        if q_len <= 0 or (skip_single and q_len == 1):
+            continue
+        pos0, rows = ctx_len - q_len, q_len * rep
+        for first in range(0, rows, 128):
+            walked = (pos0 + (min(rows, first + 128) - 1) // rep) // 64 + 1
+            work += walked * nkv
+            heaviest = max(heaviest, walked)
+    fair = max(8, -(-5 * work // (4 * SM_COUNT)))
+    return fair if heaviest > fair else 0
+
+
 def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, max_q_len: int,
                           nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
-                          skip_single: bool) -> None:
-    """bfloat16 attention of the requests that bring several tokens (csrc/attention_mma.cu, prefill)."""
-    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table)
+                          skip_single: bool, split_above: int = 0, halves: torch.Tensor | None = None) -> None:
+    """bfloat16 attention of the requests that bring several tokens (csrc/attention_mma.cu, prefill).
+    split_above > 0 (head sizes in steps of 64): a tile of 128 rows that walks more than that many tiles of 64
+    keys is computed by two CTAs, half of the keys each; `halves` (float32) holds their partial results."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, halves)
+    if split_above > 0:
+        assert hd % 64 == 0 and halves is not None and halves.dtype == torch.float32 and halves.is_contiguous()
+        assert halves.numel() >= attention_prefill_halves_floats(req_q_len.shape[0], max_q_len, nq, nkv, hd)
     assert q.dtype == torch.bfloat16 == out.dtype == k_pages.dtype and q.stride(1) == 1 and out.stride(1) == 1
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
     lib = load_family("attention_mma", {"HEAD_DIM": hd})
@@ -212,7 +247,8 @@ def attention_mma_prefill(q, out, k_pages, v_pages, req_q_start, req_q_len, req_
                                           _ptr(_int32(req_ctx_len, "req_ctx_len")),
                                           _ptr(_int32(block_table, "block_table")), block_table.shape[1],
                                           req_q_len.shape[0], max_q_len, nq, nkv, page_size, window, c_float(scale),
-                                          1 if skip_single else 0, _ptr(_status_word(q.device)), _stream()),
+                                          1 if skip_single else 0, split_above, _ptr(halves) if split_above > 0 else None,
+                                          _ptr(_status_word(q.device)), _stream()),
            f"attention_mma_prefill(head_dim={hd}, heads={nq}/{nkv})")
 
 
