@@ -542,9 +542,13 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     }
     __syncthreads();
 
-    // merge the consumer warps through shared memory (the ring is free now)
-    float* sm_o = reinterpret_cast<float*>(smem);                  // [warp][16][HD]
-    float* sm_ml = sm_o + WS_CONSUMERS * 16 * HD;                   // [warp][16][2]
+    // merge the consumer warps through shared memory (the ring is free now): rows of HD + 8 floats keep the
+    // 8-byte stores of a warp's fragment off each other's banks; only the group's `rep` rows are kept
+    constexpr int MS = HD + 8;
+    float* sm_o = reinterpret_cast<float*>(smem);                  // [warp][16][MS]
+    float* sm_ml = sm_o + WS_CONSUMERS * 16 * MS;                   // [warp][16][2]
+    float* sm_f = sm_ml + WS_CONSUMERS * 16 * 2;                    // [16][WS_CONSUMERS] weights, then [16][2] (max, sum)
+    float* sm_row = sm_f + 16 * WS_CONSUMERS;
     if (warp < WS_CONSUMERS) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -554,10 +558,10 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
         for (int n = 0; n < NTO; ++n) {
-            float* o0 = sm_o + ((size_t)(warp * 16 + r0) * HD) + n * 8 + c0;
-            float* o1 = sm_o + ((size_t)(warp * 16 + r0 + 8) * HD) + n * 8 + c0;
-            o0[0] = st.o[n][0]; o0[1] = st.o[n][1];
-            o1[0] = st.o[n][2]; o1[1] = st.o[n][3];
+            if (r0 < rep)
+                *reinterpret_cast<float2*>(sm_o + (size_t)(warp * 16 + r0) * MS + n * 8 + c0) = make_float2(st.o[n][0], st.o[n][1]);
+            if (r0 + 8 < rep)
+                *reinterpret_cast<float2*>(sm_o + (size_t)(warp * 16 + r0 + 8) * MS + n * 8 + c0) = make_float2(st.o[n][2], st.o[n][3]);
         }
         if ((lane & 3) == 0) {
             sm_ml[(warp * 16 + r0) * 2] = st.m[0];      sm_ml[(warp * 16 + r0) * 2 + 1] = st.l[0];
@@ -565,26 +569,42 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < rep * HD; idx += WS_THREADS) {
-        const int row = idx / HD, d = idx % HD;
+    if ((int)threadIdx.x < rep) {            // the warps' weights exp2(m_w - M) and the row's sum, once per row
+        const int row = threadIdx.x;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WS_CONSUMERS; ++w) M = fmaxf(M, sm_ml[(w * 16 + row) * 2]);
         const float mbase = M == -INFINITY ? 0.f : M;
-        float L = 0.f, O = 0.f;
+        float L = 0.f;
 #pragma unroll
         for (int w = 0; w < WS_CONSUMERS; ++w) {
             const float f = exp2f(sm_ml[(w * 16 + row) * 2] - mbase);
+            sm_f[row * WS_CONSUMERS + w] = f;
             L += sm_ml[(w * 16 + row) * 2 + 1] * f;
-            O += sm_o[(size_t)(w * 16 + row) * HD + d] * f;
+        }
+        sm_row[row * 2] = M;
+        sm_row[row * 2 + 1] = L;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < rep * (HD / 4); idx += WS_THREADS) {
+        const int row = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
+        float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < WS_CONSUMERS; ++w) {
+            const float f = sm_f[row * WS_CONSUMERS + w];
+            const float4 o = *reinterpret_cast<const float4*>(sm_o + (size_t)(w * 16 + row) * MS + d);
+            O.x += o.x * f; O.y += o.y * f; O.z += o.z * f; O.w += o.w * f;
         }
         const int head = g * rep + row;
         if (num_splits == 1) {
-            out[(size_t)token * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
+            const float L = sm_row[row * 2 + 1];
+            __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (size_t)token * out_stride + (size_t)head * HD + d);
+            dst[0] = __floats2bfloat162_rn(O.x / L, O.y / L);
+            dst[1] = __floats2bfloat162_rn(O.z / L, O.w / L);
         } else {
             const size_t slot = ((size_t)r * nq + head) * max_splits + split;
-            part_o[slot * HD + d] = O;
-            if (d == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+            *reinterpret_cast<float4*>(part_o + slot * HD + d) = O;
+            if (d == 0) { part_ml[slot * 2] = sm_row[row * 2]; part_ml[slot * 2 + 1] = sm_row[row * 2 + 1]; }
         }
     }
     if (num_splits == 1 || arrivals == nullptr) return;
