@@ -94,11 +94,12 @@ def test_split_k_partial_sums(M, N, K):
     assert torch.equal(again, out)        # part s is the same sum whoever computes it
 
 
-@pytest.mark.parametrize("M,half", [(8, 48), (8, 64), (8, 112), (40, 32), (64, 80), (100, 16), (128, 96), (31, 128)])
+@pytest.mark.parametrize("M,half", [(8, 48), (8, 64), (8, 112), (40, 32), (64, 80), (100, 16), (128, 96), (31, 128),
+                                    (300, 80), (257, 16), (512, 112), (260, 64)])     # from 129 rows on: pairs of CTAs
 @pytest.mark.parametrize("epilogue", ["f32", "bf16", "gelu_tanh"])
 def test_every_tile_shape_of_products_of_few_rows(M, half, epilogue):
-    """The W tile of a stage is two halves of `half` rows: every multiple of 16 the row count allows, at an N
-    and K that are multiples of nothing."""
+    """The W tile of a stage is two halves of `half` rows (one half in each CTA of a pair): every multiple of 16
+    the row count allows, at an N and K that are multiples of nothing."""
     from wllm_b200.kernels import ops
     I, K = 300, 200
     a, w = operands(M, 2 * I, K, seed=half + M)

@@ -286,25 +286,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // Both CTAs allocate and free tensor memory together (cta_group::2), and neither leaves before the other
 // has finished (cluster barrier): its shared memory and barriers are written by the other until then.
 // ------------------------------------------------------------------------------------------------
+// Each CTA's half of the W tile has `half_rows` rows (128 unless the host found that a narrower tile fills the
+// 74 pairs better, e.g. 80 for a 2,560-column product of 2,048 rows); narrower halves deepen the ring.
 struct PairRing {
-    static constexpr int STAGES = 6;
-    static constexpr int A_BYTES = 128 * BK * 2, B_BYTES = 128 * BK * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
+    static constexpr int A_BYTES = 128 * BK * 2;
+    static constexpr int RING_BYTES = 6 * (A_BYTES + 128 * BK * 2);
+    static constexpr int MAX_STAGES = 12;
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 256;
 };
-constexpr uint32_t IDESC_PAIR = umma_idesc(2 * BM, BN, false, false);
 
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
-                    int ldc, int M, int N, int K, int up_row_offset, int k_splits, int* __restrict__ status) {
-    constexpr int STAGES = PairRing::STAGES, A_BYTES = PairRing::A_BYTES, STAGE_BYTES = PairRing::STAGE_BYTES;
-    constexpr int RING_BYTES = PairRing::RING_BYTES;
+                    int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status) {
+    constexpr int A_BYTES = PairRing::A_BYTES, RING_BYTES = PairRing::RING_BYTES, MAX_STAGES = PairRing::MAX_STAGES;
+    const int STAGE_BYTES = A_BYTES + half_rows * BK * 2;
+    const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE_BYTES);
     extern __shared__ unsigned char smem_raw[];
     const uint32_t ring = (smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t bars = ring + RING_BYTES;
-    const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t full0 = bars, empty0 = bars + 8 * MAX_STAGES, tfull0 = bars + 16 * MAX_STAGES, tempty0 = tfull0 + 16;
     const uint32_t tmem_slot = tempty0 + 16;
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_addr(smem_raw)));
 
@@ -314,8 +315,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
     const int n_cols = GATED ? N / 2 : N;
-    const int tile_n = GATED ? 128 : BN;
-    constexpr int UP_COL = 128;
+    const int tile_n = GATED ? half_rows : 2 * half_rows;
+    const int UP_COL = half_rows;
+    const uint32_t idesc = umma_idesc(2 * BM, 2 * half_rows, false, false);
     const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (n_cols + tile_n - 1) / tile_n;
     const int tiles_mn = tiles_m * tiles_n, num_tiles = tiles_mn * k_splits;
     const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
@@ -333,7 +335,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot_ptr;
     const uint32_t lead_full0 = cluster_map(full0, 0), lead_tempty0 = cluster_map(tempty0, 0);
     // this CTA's half of the W tile: rows n0.. (first CTA) or the second half / the up matrix (second CTA)
-    const int w_row_offset = rank == 0 ? 0 : (GATED ? up_row_offset : 128);
+    const int w_row_offset = rank == 0 ? 0 : (GATED ? up_row_offset : half_rows);
 
     if (warp == 0) {
         // ---------------- TMA producer (one in each CTA) ----------------
@@ -395,7 +397,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_pair(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), IDESC_PAIR,
+                        tc_mma_pair(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), idesc,
                                     (kb > kb_lo || k > 0) ? 1u : 0u);
                     tc_commit_pair(empty0 + 8 * stage, 3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -532,7 +534,7 @@ static int resident_pairs() {
 
 template <int EPI>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                       int k_splits, int* status, int pairs, cudaStream_t stream) {
+                       int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -544,7 +546,7 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, in
     if (resident < 1) return WLLM_BAD_SIZE;
     if (pairs > resident) pairs = resident;
     return wllm_launch(gemm_tc_pair_kernel<EPI>, 2 * pairs, NUM_THREADS, PairRing::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
-                       up_off, k_splits, status);
+                       up_off, k_splits, half_rows, status);
 }
 
 // Number of CTA pairs of the two-CTA kernel that one device holds at once (for reports).
@@ -578,8 +580,8 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc
 // C = A W^T.  epilogue 0: bf16 C [M, N]; 1: fp32 C [M, N]; 2 / 3: W = [gate; up] ([N, K], N even), bf16 C [M, N/2]
 // = gelu_tanh(gate) * up / silu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
 // k_splits > 1 needs epilogue 1 and a C of k_splits slabs [M, ldc]; every part must hold at least one block of K.
-// half_rows (a multiple of 16 up to 128; 0 = 128) sets the tile of products of at most 128 rows: 2 * half_rows
-// output columns, or half_rows columns of the gated output.
+// half_rows (a multiple of 16 up to 128; 0 = 128) sets the width of a tile: 2 * half_rows output columns, or
+// half_rows columns of the gated output (by 128 rows, or 256 rows on a pair of CTAs).
 WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
                                int epilogue, int k_splits, int half_rows, int* status, int max_ctas, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return WLLM_OK;
@@ -593,7 +595,7 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     const bool gated = epilogue == EPI_GATED_GELU || epilogue == EPI_GATED_SILU;
     if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
     const bool pair = M > BM && max_ctas >= 2 && pair_enabled();
-    if (half_rows == 0 || pair) half_rows = 128;
+    if (half_rows == 0) half_rows = 128;
     if (half_rows < 16 || half_rows > 128 || half_rows % 16 != 0) return WLLM_BAD_SIZE;
     CUtensorMap ma, mw;
     int r = tensor_map(a, M, K, lda, a_rows_for(M), &ma);
@@ -605,10 +607,10 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
         const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((n_cols + tile_n - 1) / tile_n) * k_splits;
         const int pairs = tiles < max_ctas / 2 ? tiles : max_ctas / 2;
         switch (epilogue) {
-            case EPI_BF16: return launch_pair<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, 1, status, pairs, stream);
-            case EPI_F32: return launch_pair<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, status, pairs, stream);
-            case EPI_GATED_GELU: return launch_pair<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, pairs, stream);
-            case EPI_GATED_SILU: return launch_pair<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, status, pairs, stream);
+            case EPI_BF16: return launch_pair<EPI_BF16>(ma, mw, c, ldc, M, N, K, 0, 1, half_rows, status, pairs, stream);
+            case EPI_F32: return launch_pair<EPI_F32>(ma, mw, c, ldc, M, N, K, 0, k_splits, half_rows, status, pairs, stream);
+            case EPI_GATED_GELU: return launch_pair<EPI_GATED_GELU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
+            case EPI_GATED_SILU: return launch_pair<EPI_GATED_SILU>(ma, mw, c, ldc, M, N, K, N / 2, 1, half_rows, status, pairs, stream);
         }
         return WLLM_BAD_SIZE;
     }

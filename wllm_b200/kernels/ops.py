@@ -300,6 +300,8 @@ def tile_plan(M: int, N: int, K: int, gated: bool = False, may_split: bool = Tru
     sums loads that many at once).  Chosen so that tiles x parts fill the SMs evenly: the cost of a choice is
     the bytes of W that the busiest CTA streams, plus a fixed price per tile and a little per part."""
     if M > 128:
+        # pairs of CTAs on 256 x 256 tiles.  Narrower tiles were measured at the one shape where they fill the
+        # pairs better (2,048 x 2,560: 80 tiles on 74 pairs): within the noise of the full width, so no gain.
         return 128, 1
     least = 48 if M <= 32 else (32 if M <= 64 else 16)     # a stage must hold the 128 rows the tensor core reads at A
     kblocks = -(-K // 64)
