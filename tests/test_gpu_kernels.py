@@ -269,6 +269,7 @@ MMA_CASES = ATTN_CASES + [
     (8, 1, 256, 16, [1030], [1030]),
     (16, 16, 256, 32, [200, 77], [5, 77]),
     (4, 2, 96, 16, [500, 333, 2], [1, 300, 2]),
+    (4, 2, 128, 32, [700, 90], [300, 90]),          # head size 128, tiles of 256 rows on pairs of CTAs
 ]
 
 

@@ -1161,6 +1161,272 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         tc_dealloc(tmem_base, 512);
     }
 }
+
+#if (HEAD_DIM % 128 == 0)
+// --------------------------------------------------------------------------------------
+// prefill on pairs of CTAs: 256 query rows a tile, score tiles of 128 keys
+// (head sizes in steps of 128: each CTA holds half of the head's columns of V in whole 64-column blocks)
+// --------------------------------------------------------------------------------------
+// The tensor core takes an instruction of N = 64 no faster than one of N = 128, so the sixteen score products
+// of a 64-key tile cost the kernel above as much as its output products.  Score tiles of 128 keys need a
+// second 128-column score buffer, which tensor memory has beside a 256-column O only when Q moves back to
+// shared memory, and shared memory has room for Q and 128-key stages only when two CTAs share the keys and
+// values: a cluster of two CTAs takes 256 query rows (128 each, with its own Q, O, scores and softmax), and
+// tcgen05.mma.cta_group::2, issued by the first CTA for both, reads half of every operand B from each:
+//   S = Q K^T   M 256, N 128 keys, K = head size; each CTA holds 64 of the 128 keys of a stage;
+//   O += P V    M 256, N = head size, K 128 keys; P from tensor memory (over the scores it came from),
+//               V MN-major, each CTA holding half of the head's columns for all 128 keys.
+// Barriers as in the two-CTA GEMM: `full` barriers (and q_full, p_full) live in the first CTA and are
+// arrived on by both; `empty`, s_full and pv_done exist in both and are arrived on by commit multicast.
+// Both CTAs allocate and free tensor memory together and pass a cluster barrier before they leave.
+constexpr int PR_BN = 128, PR_STAGES = 2;
+constexpr int PR_Q_BYTES = TC_BM * ROWB;                   // this CTA's 128 query rows
+constexpr int PR_K_BYTES = (PR_BN / 2) * ROWB;             // 64 keys x head size
+constexpr int PR_V_BYTES = PR_BN * (ROWB / 2);             // 128 keys x half the head size
+constexpr int PR_SMEM = 1024 + PR_Q_BYTES + PR_STAGES * (PR_K_BYTES + PR_V_BYTES) + 256;
+constexpr uint32_t IDESC_PR_S = umma_idesc(2 * TC_BM, PR_BN, false, false);
+constexpr uint32_t IDESC_PR_PV = umma_idesc(2 * TC_BM, HD, false, true);
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                    const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
+                    const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
+                    int skip_single, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    pdl_begin();
+    const int g = blockIdx.y, r = blockIdx.z;
+    const int q_len = req_q_len[r];
+    if (q_len <= 0 || (skip_single && q_len == 1)) return;             // the same for both CTAs of a pair
+    const int rep = nq / nkv, rows = q_len * rep;
+    const uint32_t rank = cluster_ctarank();
+    const int tile = (int)(gridDim.x >> 1) - 1 - (int)(blockIdx.x >> 1);
+    if (tile * 2 * TC_BM >= rows) return;
+    const int row0 = tile * 2 * TC_BM + (int)rank * TC_BM;             // may lie past the end: then all rows are masked
+    const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_s = base, k_s = q_s + PR_Q_BYTES, v_s = k_s + PR_STAGES * PR_K_BYTES;
+    const uint32_t bars = v_s + PR_STAGES * PR_V_BYTES;
+    const uint32_t k_full = bars, k_empty = k_full + 8 * PR_STAGES, v_full = k_empty + 8 * PR_STAGES;
+    const uint32_t v_empty = v_full + 8 * PR_STAGES, s_full = v_empty + 8 * PR_STAGES;
+    const uint32_t q_full = s_full + 16, p_full = q_full + 8, pv_done = p_full + 8, tmem_slot = pv_done + 8;
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+    // the keys that the pair's 256 rows see
+    const int last_row = min(rows, (tile + 1) * 2 * TC_BM) - 1;
+    const int pos_hi = pos0 + last_row / rep, pos_lo = pos0 + (tile * 2 * TC_BM) / rep;
+    const int key_lo = window > 0 ? max(0, pos_lo - window + 1) : 0, key_hi = pos_hi + 1;
+    const int t0 = key_lo / PR_BN, t1 = (key_hi + PR_BN - 1) / PR_BN, T = t1 - t0;
+    const int page_shift = 31 - __clz(page_size);
+    const int* table = block_table + (size_t)r * max_pages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PR_STAGES; ++s) {
+            mbar_init(k_full + 8 * s, 2); mbar_init(k_empty + 8 * s, 1);
+            mbar_init(v_full + 8 * s, 2); mbar_init(v_empty + 8 * s, 1);
+        }
+        mbar_init(s_full, 1); mbar_init(s_full + 8, 1);
+        mbar_init(q_full, 8);
+        mbar_init(p_full, 8);
+        mbar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tc_alloc_pair(tmem_slot, 512);
+    tc_fence_before();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+    const uint32_t lead_k_full = cluster_map(k_full, 0), lead_v_full = cluster_map(v_full, 0);
+    const uint32_t lead_q_full = cluster_map(q_full, 0), lead_p_full = cluster_map(p_full, 0);
+
+    if (warp == 0 || warp == 6) {
+        // ---------------- TMA producers: warp 0 this CTA's half of the key tiles, warp 6 of the value tiles ----------------
+        if (lane == 0) {
+            const int kv = warp == 6;
+            const uint32_t full0 = kv ? lead_v_full : lead_k_full, empty0 = kv ? v_empty : k_empty;
+            const uint32_t ring = kv ? v_s : k_s, stage_bytes = kv ? PR_V_BYTES : PR_K_BYTES;
+            const CUtensorMap* map = kv ? &v_map : &k_map;
+            const int box_rows = page_size < 64 ? page_size : 64;
+            // keys: rows [64 * rank, +64) of the tile, all columns; values: all 128 rows, columns [HD/2 * rank, +HD/2)
+            const int row_lo = kv ? 0 : 64 * (int)rank, row_n = kv ? PR_BN : 64;
+            const int col_lo = kv ? (HD / 2) * (int)rank : 0, col_blocks = kv ? HD / 128 : HD / 64;
+            bool ok = true;
+            int n = 0;
+            for (; n < T && ok; ++n) {
+                const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1, tile_start = (t0 + n) * PR_BN + row_lo;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
+                const uint32_t bar = full0 + 8 * s, dst = ring + s * stage_bytes;
+                mbar_expect_tx_cluster(bar, stage_bytes);
+                for (int r0 = 0; r0 < row_n; r0 += box_rows) {
+                    const int key = tile_start + r0, index = key >> page_shift;
+                    int page = index < max_pages ? table[index] : 0;
+                    if (page < 0) page = 0;
+                    const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+                    for (int cb = 0; cb < col_blocks; ++cb)
+                        tma_load_2d_pair(dst + cb * (row_n * 128) + r0 * 128, map, bar, col_lo + cb * 64, row);
+                }
+            }
+            for (int k = 0; k < PR_STAGES && ok; ++k, ++n) {          // nothing in flight at the exit
+                const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) ok = false;
+            }
+            if (!ok) atomicExch(status, GAVE_UP_TC_LOAD);
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: the first CTA's, for both ----------------
+        if (lane == 0 && rank == 0) {
+            bool ok = mbar_wait(q_full, 0);
+            tc_fence_after();
+            auto issue_scores = [&](int n) -> bool {       // S(n) = Q K(n)^T into score buffer n % 2
+                const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1;
+                if (!mbar_wait(k_full + 8 * s, ph)) return false;
+                tc_fence_after();
+                const uint32_t d = tmem_base + TC_S_COL + (n & 1) * PR_BN, kb = k_s + s * PR_K_BYTES;
+#pragma unroll
+                for (int kt = 0; kt < HD / 16; ++kt)
+                    tc_mma_pair(d, smem_desc(q_s + (kt >> 2) * (TC_BM * 128) + (kt & 3) * 32),
+                                smem_desc(kb + (kt >> 2) * (64 * 128) + (kt & 3) * 32), IDESC_PR_S, kt > 0 ? 1u : 0u);
+                tc_commit_pair(k_empty + 8 * s, 3);
+                tc_commit_pair(s_full + 8 * (n & 1), 3);
+                return true;
+            };
+            ok = ok && issue_scores(0);
+            for (int n = 0; n < T && ok; ++n) {
+                if (n + 1 < T && !issue_scores(n + 1)) { ok = false; break; }
+                const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1;
+                if (!mbar_wait(v_full + 8 * s, ph) || !mbar_wait(p_full, n & 1)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t vb = v_s + s * PR_V_BYTES, pa = tmem_base + TC_S_COL + (n & 1) * PR_BN;
+#pragma unroll
+                for (int kk = 0; kk < PR_BN / 16; ++kk)
+                    tc_mma_ts_pair(tmem_base, pa + kk * 8, smem_desc_mn(vb + kk * (16 * 128), PR_BN * 128), IDESC_PR_PV,
+                                   (n > 0 || kk > 0) ? 1u : 0u);
+                tc_commit_pair(v_empty + 8 * s, 3);
+                tc_commit_pair(pv_done, 3);
+            }
+            if (!ok) atomicExch(status, GAVE_UP_TC_MMA);
+        }
+    } else {
+        // ---------------- softmax: one thread per row of this CTA ----------------
+        const int quarter = warp & 3, row = quarter * 32 + lane, m_row = row0 + row;
+        const int epi_tid = threadIdx.x - 64;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        // this CTA's query rows, in the layout the tensor core reads (the same swizzle as a box copy)
+        for (int idx = epi_tid; idx < TC_BM * CPR; idx += 128) {
+            const int rr = idx / CPR, chunk = idx % CPR, m = row0 + rr;
+            const bool valid = m < rows;
+            const bf16* src = valid ? q + (size_t)(q_start + m / rep) * q_stride + (size_t)(g * rep + m % rep) * HD + chunk * 8 : q;
+            cp_async16(q_s + swz<TC_BM>(rr, chunk), src, valid);
+        }
+        cp_commit();
+        cp_wait<0>();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(lead_q_full);
+
+        const int pos_row = m_row < rows ? pos0 + m_row / rep : -1;            // a row past the end sees no key
+        const int first_row = window > 0 ? max(0, pos_row - window + 1) : 0;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int n = 0; n < T; ++n) {
+            const int b = n & 1, ph = (n >> 1) & 1, key0 = (t0 + n) * PR_BN;
+            if (!mbar_wait(s_full + 8 * b, ph)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sv[4][32];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) tc_ld32(t_lane + TC_S_COL + b * PR_BN + 32 * h, sv[h]);
+            tc_wait_ld();
+            const bool inner = __all_sync(0xffffffffu, key0 + PR_BN - 1 <= pos_row && key0 >= first_row);
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (inner) {
+#pragma unroll
+                for (int c = 0; c < PR_BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c >> 5][c & 31]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < PR_BN; ++c) {
+                    const int key = key0 + c;
+                    const float v = (key <= pos_row && key >= first_row) ? __uint_as_float(sv[c >> 5][c & 31]) : -INFINITY;
+                    sv[c >> 5][c & 31] = __float_as_uint(v);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], v);
+                }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float m_tile = fmaxf(m_run, mx * scale2);
+            const float m_new = m_tile > m_run + TC_MAX_SLACK ? m_tile : m_run;      // lazily, as in the kernel above
+            const float mbase = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = fast_exp2(m_run - mbase);
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t packed[2][32];
+#pragma unroll
+            for (int c = 0; c < PR_BN; c += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c >> 5][c & 31]), scale2, -mbase));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sv[(c + 1) >> 5][(c + 1) & 31]), scale2, -mbase));
+                sum4[(c >> 1) & 3] += p0 + p1;
+                packed[c >> 6][(c >> 1) & 31] = pack_bf16(p0, p1);
+            }
+            l_run = l_run * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            const bool changed = m_new > m_run;
+            m_run = m_new;
+            // P over the scores this thread has just read: keys (2j, 2j + 1) in column j of the buffer
+            tc_st32(t_lane + TC_S_COL + b * PR_BN, packed[0]);
+            tc_st32(t_lane + TC_S_COL + b * PR_BN + 32, packed[1]);
+            if (n > 0) {
+                if (!mbar_wait(pv_done, (n - 1) & 1)) { ok = false; break; }     // O of the tile before is complete
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, changed)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t ov[32];
+                        tc_ld32(t_lane + c0, ov);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * corr);
+                        tc_st32(t_lane + c0, ov);
+                    }
+                }
+            }
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(lead_p_full);
+        }
+        if (ok && !mbar_wait(pv_done, (T - 1) & 1)) ok = false;
+        ok = __all_sync(0xffffffffu, ok);        // the tensor-memory loads below are collective: all lanes or none
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.0f / l_run;
+            bf16* dst = m_row < rows ? out + (size_t)(q_start + m_row / rep) * out_stride + (size_t)(g * rep + m_row % rep) * HD : nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t ov[32];
+                tc_ld32(t_lane + c0, ov);
+                tc_wait_ld();
+                if (dst) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(ov[c]) * inv, __uint_as_float(ov[c + 1]) * inv);
+                        o.y = pack_bf16(__uint_as_float(ov[c + 2]) * inv, __uint_as_float(ov[c + 3]) * inv);
+                        o.z = pack_bf16(__uint_as_float(ov[c + 4]) * inv, __uint_as_float(ov[c + 5]) * inv);
+                        o.w = pack_bf16(__uint_as_float(ov[c + 6]) * inv, __uint_as_float(ov[c + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = o;
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(status, GAVE_UP_TC_SOFTMAX);
+        }
+    }
+    tc_fence_before();
+    cluster_sync();                       // nothing of either CTA is still in use by the other
+    if (warp == 1) {
+        tc_fence_after();
+        tc_dealloc_pair(tmem_base, 512);
+    }
+}
+#endif
 #endif
 
 // --------------------------------------------------------------------------------------
@@ -1339,6 +1605,9 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
 #if (HEAD_DIM % 64 == 0)
     static bool use_tc = false;
 #endif
+#if (HEAD_DIM % 128 == 0)
+    static bool use_pair = false;
+#endif
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PRE_SMEM);
         if (e != cudaSuccess) return 1000 + (int)e;
@@ -1348,10 +1617,25 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
         const char* legacy = getenv("WLLM_ATTENTION_MMA");       // =1: the mma.sync kernel, for comparison
         use_tc = !(legacy && legacy[0] == '1');
 #endif
+#if (HEAD_DIM % 128 == 0)
+        e = cudaFuncSetAttribute(prefill_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PR_SMEM);
+        if (e != cudaSuccess) return 1000 + (int)e;
+        const char* single = getenv("WLLM_ATTENTION_PAIR");      // =0: one CTA a tile always
+        use_pair = !(single && single[0] == '0');
+#endif
         configured = true;
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
 #if (HEAD_DIM % 64 == 0)
+#if (HEAD_DIM % 128 == 0)
+    // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
+    if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
+        const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
+        return wllm_launch(prefill_pair_kernel, dim3(2 * pair_tiles, nkv, requests), TC_THREADS, PR_SMEM, stream,
+                           (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
+                           block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
+    }
+#endif
     if (use_tc && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         int* arrivals = nullptr;
         if (split_above > 0) {

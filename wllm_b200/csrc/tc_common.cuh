@@ -150,6 +150,14 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, ui
                    "r"(0), "r"(0), "r"(0), "r"(0)
                  : "memory");
 }
+// the same with the A operand in tensor memory (each CTA's own rows, at the same address in both)
+__device__ __forceinline__ void tc_mma_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0),
+                   "r"(0), "r"(0), "r"(0), "r"(0)
+                 : "memory");
+}
 // arrives on the barrier at this offset in every CTA of `cta_mask` once the products issued so far are done
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
