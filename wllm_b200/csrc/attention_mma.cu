@@ -329,7 +329,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
               int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
-    const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+    const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
@@ -451,7 +451,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     pdl_launch_dependents();
     // The step's index arrays were copied before its first kernel started, and no kernel of this step writes
     // a key below the new token's place: they may be read before this kernel waits for its predecessor.
-    const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+    const int split = blockIdx.z, g = blockIdx.y, r = blockIdx.x;     // CTAs start request by request, the last (shortest) splits last
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
@@ -1537,7 +1537,8 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     const int bad = check_common(q, q_stride, out, out_stride, k_pages, v_pages, nq, nkv, page_size, pool_pages);
     if (bad) return bad;
     const int tile = USE_TMA ? WS_BN : BN;      // splits are whole tiles of the kernel that runs
-    if (nq / nkv > 16 || split_keys < BN || split_keys % tile != 0 || max_splits < 1 || max_splits > MERGE_MAX_SPLITS)
+    if (nq / nkv > 16 || split_keys < BN || split_keys % tile != 0 || max_splits < 1 || max_splits > MERGE_MAX_SPLITS ||
+        nkv > 65535)
         return WLLM_BAD_SIZE;
     CUtensorMap km, vm;
     const long long rows = pool_pages * nkv * page_size;
@@ -1561,13 +1562,13 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
         // the last CTA of each (request, kv head) merges the splits itself where a counter is to be had
         int* arrivals = (long long)requests * nkv <= ARRIVAL_SLOTS && max_splits > 1 && max_splits <= FUSED_MERGE_SPLITS
                             ? arrivals_address() : nullptr;
-        st = wllm_launch(decode_ws_kernel, dim3(max_splits, nkv, requests), WS_THREADS, WS_SMEM, stream,
+        st = wllm_launch(decode_ws_kernel, dim3(requests, nkv, max_splits), WS_THREADS, WS_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                          block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o,
                          part_ml, arrivals, status);
         if (arrivals != nullptr) return st;
     } else
-        st = wllm_launch(decode_kernel, dim3(max_splits, nkv, requests), NTHREADS, DEC_SMEM, stream,
+        st = wllm_launch(decode_kernel, dim3(requests, nkv, max_splits), NTHREADS, DEC_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                          req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window,
                          scale * LOG2E, split_keys, max_splits, part_o, part_ml, status);

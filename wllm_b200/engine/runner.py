@@ -73,12 +73,9 @@ class StepContext:
         decode = self.num_single > 0 and nq // nkv <= 16
         if decode:
             R = self.n_requests
-            # one CTA fits on an SM: split every (request, kv head) so that all CTAs run in one wave,
-            # in whole tiles (32 keys in the warp-specialised kernel, else 64) and not below 128 keys
-            per_head = max(1, SM_COUNT // (R * nkv))
-            tile = 32 if hd % 64 == 0 else 64
-            split_keys = max(128, -(-(-(-self.max_ctx // per_head)) // tile) * tile)
-            max_splits = max(1, -(-self.max_ctx // split_keys))
+            # one CTA fits on an SM: every (request, kv head) is cut into parts so that the CTAs finish together
+            # (planned for the context rounded up to 512 keys, so that a growing context seldom needs a new plan)
+            split_keys, max_splits = ops.decode_split_plan(R * nkv, -(-self.max_ctx // 512) * 512, 32 if hd % 64 == 0 else 64)
             scratch = self.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
                                   torch.float32)
             ops.attention_mma_decode(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,

@@ -95,10 +95,7 @@ def attention(args, decode: bool) -> None:
     ctxs = torch.full((R,), ctx, dtype=torch.int32, device=DEV)
     scale = 1.0 / math.sqrt(hd)
     if decode:
-        per_head = max(1, 148 // (R * nkv))
-        tile = 32 if hd % 64 == 0 else 64
-        split_keys = max(128, -(-(-(-ctx // per_head)) // tile) * tile)
-        max_splits = -(-ctx // split_keys)
+        split_keys, max_splits = ops.decode_split_plan(R * nkv, ctx, 32 if hd % 64 == 0 else 64)
         scratch = torch.empty(ops.attention_mma_scratch_floats(R, nq, hd, max_splits), device=DEV)
 
         def run():
