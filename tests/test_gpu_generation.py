@@ -133,8 +133,10 @@ def test_the_engine_refuses_to_run_without_cuda_or_with_bad_ids(folders):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_captured_decode_steps_change_nothing(folders, dtype):
-    prompts = prompts_of("B", (5, 40, 77, 3), seed=6)
-    sp = SamplingParams(temperature=0.9, seed=5, max_tokens=40, ignore_eos=True)
+    """Five requests that end at different lengths: the captured steps serve 5 in a capture for 6 (one request
+    that brings no token is appended), then 4, 3, 2 and 1."""
+    prompts = prompts_of("B", (5, 40, 77, 3, 21), seed=6)
+    sp = [SamplingParams(temperature=0.9, seed=5, max_tokens=n, ignore_eos=True) for n in (40, 33, 40, 12, 25)]
     kw = dict(dtype=dtype, block_size=32, num_blocks=24, chunked_prefill_tokens=32)
     plain_run = llm(folders["B"], **kw).generate(prompts, sp)
     graphed = llm(folders["B"], cuda_graphs=True, **kw)

@@ -51,6 +51,7 @@ class StepContext:
         self.group_tables: list = []
         self.host = None   # the same arrays on the host, for launch decisions
         self.num_single = self.num_multi = 0     # requests with one token / with several
+        self._share_plans: dict = {}             # prefill attention's tile sharing, by head layout
         self.max_q_len = self.max_ctx = 0        # bounds that size the attention grids
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
@@ -88,9 +89,17 @@ class StepContext:
 
     def _shared_tiles(self, nq: int, nkv: int, hd: int, skip_single: bool):
         """Whether this step's prefill attention shares its heavy tiles between two CTAs (ops.prefill_share_plan),
-        and the buffer for their partial results."""
-        split_above = ops.prefill_share_plan(self.host["req_q_len"].tolist(), self.host["req_ctx_len"].tolist(), nq, nkv,
-                                             hd, skip_single)
+        and the buffer for their partial results.  Worked out once a step and head layout, not once a layer;
+        head sizes that run on pairs of CTAs (steps of 128, more than one tile of rows) never share."""
+        key = (nq, nkv, hd, skip_single)
+        if key not in self._share_plans:
+            if hd % 128 == 0 and self.max_q_len * (nq // nkv) > 128:
+                plan = 0
+            else:
+                plan = ops.prefill_share_plan(self.host["req_q_len"].tolist(), self.host["req_ctx_len"].tolist(), nq, nkv,
+                                              hd, skip_single)
+            self._share_plans[key] = plan
+        split_above = self._share_plans[key]
         if split_above <= 0:
             return 0, None
         floats = ops.attention_prefill_halves_floats(self.n_requests, self.max_q_len, nq, nkv, hd)
@@ -125,13 +134,20 @@ class ModelRunner:
         return buf[:n].view(shape)
 
     # -- batch building --------------------------------------------------------------
-    def _build(self, entries: list, table_width: int | None = None, device_tokens=None) -> StepContext:
+    def _build(self, entries: list, table_width: int | None = None, device_tokens=None,
+               pad_requests: int | None = None) -> StepContext:
+        """`pad_requests` (a decode step under a captured graph): the arrays are laid out for that many requests;
+        the ones behind the real entries bring no token (q_len 0, no cache slot), so every kernel passes them
+        by, and the logits of all rows are wanted (the caller keeps the real ones)."""
         cache, ps = self.cache, self.cache.page_size
-        G, R = len(cache.groups), len(entries)
+        G, real = len(cache.groups), len(entries)
         lens = [len(e.tokens) for e in entries]
-        N = sum(lens)
-        M = sum(len(e.want) for e in entries)
         P = table_width or max(1, max(len(t) for e in entries for t in e.cache.tables) if G else 1)
+        if pad_requests is not None:
+            assert sum(lens) == real and pad_requests >= real
+            R = N = M = pad_requests
+        else:
+            R, N, M = real, sum(lens), sum(len(e.want) for e in entries)
 
         def pad(n):
             return (n + 3) & ~3
@@ -152,22 +168,26 @@ class ModelRunner:
         if N == R:
             # every request brings one token (a decode step): whole columns at once, tables from cached copies
             bases = [e.cache.num_tokens for e in entries]
-            view("token_ids")[:] = [e.tokens[0] for e in entries]
-            view("positions")[:] = bases
+            view("token_ids")[:real] = [e.tokens[0] for e in entries]
+            view("positions")[:real] = bases
             ar = np.arange(R, dtype=np.int32)
             view("token_req")[:] = ar
             view("req_q_start")[:] = ar
-            view("req_q_len")[:] = 1
-            view("req_ctx_len")[:] = np.asarray(bases, dtype=np.int32) + 1
-            view("req_slot")[:] = [e.cache.slot for e in entries]
+            view("req_q_len")[:real] = 1
+            view("req_ctx_len")[:real] = np.asarray(bases, dtype=np.int32) + 1
+            view("req_slot")[:real] = [e.cache.slot for e in entries]
             for g in range(G):
-                view(f"slots{g}")[:] = [e.cache.tables[g][b // ps] * ps + b % ps for e, b in zip(entries, bases)]
+                view(f"slots{g}")[real:] = -1
+                view(f"slots{g}")[:real] = [e.cache.tables[g][b // ps] * ps + b % ps for e, b in zip(entries, bases)]
                 rows2d = view(f"table{g}").reshape(R, P)
                 for r, e in enumerate(entries):
                     t = self._table_copy(e.cache, g)
                     rows2d[r, :t.shape[0]] = t
-            for r, e in enumerate(entries):
-                wants.extend(r + w for w in e.want)
+            if pad_requests is not None:
+                wants.extend(range(R))
+            else:
+                for r, e in enumerate(entries):
+                    wants.extend(r + w for w in e.want)
             entries_loop = ()
         else:
             entries_loop = enumerate(entries)
@@ -203,7 +223,7 @@ class ModelRunner:
         ctx.n_tokens, ctx.n_requests, ctx.host = N, R, {k: view(k) for k, _ in sizes}
         ctx.host["max_pages"] = P
         ctx.num_single = sum(1 for n in lens if n == 1)
-        ctx.num_multi = R - ctx.num_single
+        ctx.num_multi = real - ctx.num_single
         ctx.max_q_len = max(lens)
         # under a captured graph the bound must not depend on the batch's contents: the table's reach
         ctx.max_ctx = table_width * ps if table_width else max(e.cache.num_tokens + n for e, n in zip(entries, lens))
@@ -274,8 +294,11 @@ class ModelRunner:
         width = 8
         while width < widest:
             width *= 2
-        key = (len(entries), width)
-        ctx = self._build(entries, table_width=width, device_tokens=device_tokens)
+        bucket = 1                      # 1, 2, 3, 4, 6, 8, 12, 16, 24, 32, ...: a capture serves every count up to its size
+        while bucket < len(entries):
+            bucket = bucket * 3 // 2 if bucket & (bucket - 1) == 0 and bucket > 1 else (bucket * 4 // 3 if bucket > 2 else bucket + 1)
+        key = (bucket, width)
+        ctx = self._build(entries, table_width=width, device_tokens=device_tokens, pad_requests=bucket)
         rec = self._graphs.get(key)
         if rec is None:
             arena, saved = {}, self._arena
@@ -295,7 +318,7 @@ class ModelRunner:
             self._graphs[key] = rec
         rec["graph"].replay()
         self.graph_launches += rec["launches"]
-        return rec["logits"]
+        return rec["logits"][:len(entries)]
 
     # -- the step ----------------------------------------------------------------------
     @torch.inference_mode()

@@ -180,31 +180,27 @@ def attention_mma_scratch_floats(requests: int, nq: int, hd: int, max_splits: in
 def decode_split_plan(heads: int, max_ctx: int, tile: int) -> tuple:
     """(split_keys, max_splits) for the decode attention of `heads` (request, key/value head) pairs with up to
     max_ctx keys each.  Every pair is cut into parts of split_keys keys (whole tiles, at least 128) plus a
-    shorter rest, one CTA a part, and the CTAs start longest first (the rests last).  Part sizes between one
-    part more and one part fewer than an SM each are tried, and the one that finishes first on 148 SMs is
-    taken: with 64 pairs of 8,118 keys, parts of 3,648 and rests of 822 (the rests fill the twenty SMs that
-    the whole parts leave) finish a tenth earlier than two equal parts."""
-    import heapq
+    shorter rest, one CTA a part, and the CTAs start longest first (the rests last).  Two part sizes are
+    weighed by when their last CTA ends on 148 SMs: equal parts, one an SM at most; and parts of the SMs'
+    even share of all keys, whose short rests run on the SMs that the whole parts leave free."""
     heads = max(1, heads)
-    first = max(1, SM_COUNT // heads)
-    low = max(128, (max_ctx // (first + 2)) // tile * tile)
-    high = max(low, -(-(-(-max_ctx // max(1, first - 1))) // tile) * tile)
-    step = tile * max(1, (high - low) // tile // 96)           # about a hundred sizes at most
-    best = None
-    for keys in range(low, high + 1, step):
+    per_cta = 2 * tile                                          # a CTA costs about two tiles beside its keys
+
+    def up(keys):
+        return max(128, -(-keys // tile) * tile)
+
+    def finish(keys):
         splits = -(-max_ctx // keys)
-        if splits > 256:
-            continue
-        rest = max_ctx - (splits - 1) * keys
-        free = [0] * SM_COUNT                                  # each CTA goes to the SM that is free first
-        finish = 0
-        for size in [keys] * ((splits - 1) * heads) + [rest] * heads:      # in starting order
-            end = heapq.heappop(free) + size + 2 * tile        # a CTA costs about two tiles beside its keys
-            finish = max(finish, end)
-            heapq.heappush(free, end)
-        if best is None or finish < best[0]:
-            best = (finish, keys, splits)
-    return best[1], best[2]
+        rest, whole = max_ctx - (splits - 1) * keys, (splits - 1) * heads
+        if whole + heads <= SM_COUNT:
+            return (keys if splits > 1 else rest) + per_cta
+        if whole < SM_COUNT:
+            return max(keys + per_cta, -(-heads // (SM_COUNT - whole)) * (rest + per_cta))
+        return -(-(whole + heads) // SM_COUNT) * (keys + per_cta)
+    equal = up(-(-max_ctx // max(1, SM_COUNT // heads)))
+    share = min(up(max_ctx), up(-(-max_ctx * heads // SM_COUNT)))
+    keys = min((equal, share), key=lambda k: (finish(k), -k))
+    return keys, -(-max_ctx // keys)
 
 
 def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, nq: int, nkv: int,

@@ -37,6 +37,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--async-scheduling", action="store_true", help="launch each step before the previous step's tokens are read")
     args = ap.parse_args(argv)
 
     from .. import LLM, SamplingParams
@@ -51,7 +52,8 @@ def main(argv=None) -> int:
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lengths]
     blocks = sum(-(-(n + args.new_tokens) // args.block_size) for n in lengths) + 1
     llm = LLM(None, config=cfg, random_seed=1, dtype=args.dtype, block_size=args.block_size, num_blocks=blocks,
-              chunked_prefill_tokens=args.chunk, max_num_seqs=args.requests, cuda_graphs=not args.no_graphs)
+              chunked_prefill_tokens=args.chunk, max_num_seqs=args.requests, cuda_graphs=not args.no_graphs,
+              async_scheduling=args.async_scheduling)
     sp = SamplingParams(temperature=0.0, max_tokens=args.new_tokens, ignore_eos=True)
     llm.generate(prompts[:2], SamplingParams(max_tokens=4, ignore_eos=True))        # warm-up: kernels, graphs
     torch.cuda.synchronize()
