@@ -50,7 +50,14 @@ def _ptr(t) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream of the current device (it changes under a graph capture, so it is looked up at every
+    launch; the raw lookup costs a fraction of a microsecond where the Stream object costs fifteen)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
