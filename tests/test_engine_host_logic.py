@@ -38,3 +38,38 @@ def test_every_cut_matches_plain(setups, monkeypatch, name, mode):
     assert runner.cache.free_pages() == [pages]
     if mode == "mixed":
         assert runner.cache.groups[0].pool.takes > pages, "the trace must use pages again"
+
+
+# ---- launch plans worked out on the host (pure functions of sizes) ----
+
+def test_decode_split_plan_covers_the_context_in_whole_tiles():
+    from wllm_b200.kernels import ops
+    for heads in (1, 3, 8, 16, 31, 64, 128, 1000):
+        for ctx in (1, 64, 129, 300, 4096, 8118, 100000):
+            for tile in (32, 64):
+                keys, splits = ops.decode_split_plan(heads, ctx, tile)
+                assert keys >= 128 and keys % tile == 0 and 1 <= splits <= 256 or ctx > 128 * 256
+                assert (splits - 1) * keys < ctx <= splits * keys       # no empty part, every key covered
+    # few pairs of many keys: about one part an SM; many pairs: one part each
+    assert ops.decode_split_plan(8, 8192, 32) == (448, 19)
+    assert ops.decode_split_plan(1000, 4096, 32)[1] == 1
+
+
+def test_tile_plan_of_products_of_few_rows():
+    from wllm_b200.kernels import ops
+    for M in (1, 8, 32, 33, 64, 65, 128):
+        for N, K, gated in ((2048, 2048, False), (2560, 2048, False), (2048, 16384, False), (32768, 2048, True), (300, 200, False)):
+            half, parts = ops.tile_plan(M, N, K, gated, not gated)
+            assert half % 16 == 0 and (48 if M <= 32 else 32 if M <= 64 else 16) <= half <= 128
+            kblocks = -(-K // 64)
+            assert 1 <= parts <= 16 and -(-kblocks // parts) * (parts - 1) < kblocks
+    assert ops.tile_plan(300, 2048, 2048) == (128, 1)             # more than 128 rows: pairs of CTAs, full width
+
+
+def test_prefill_share_plan_only_for_grids_that_fit_the_sms_once():
+    from wllm_b200.kernels import ops
+    assert ops.prefill_share_plan([2048], [2048], 8, 1, 64, False) == 18       # 128 tiles, the heaviest walks 32
+    assert ops.prefill_share_plan([2048], [16384], 8, 1, 64, False) == 0       # every tile walks about the same
+    assert ops.prefill_share_plan([2048] * 4, [2048] * 4, 8, 1, 64, False) == 0   # more CTAs than SMs anyway
+    assert ops.prefill_share_plan([1, 1], [500, 600], 8, 1, 64, True) == 0     # single tokens are the decode kernel's
+    assert ops.prefill_share_plan([2048], [2048], 8, 1, 48, False) == 0        # head sizes without the tcgen05 kernel
