@@ -53,6 +53,7 @@ constexpr int NTHREADS = NWARPS * 32;
 constexpr int TILE_BYTES = BN * ROWB;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr bool USE_TMA = (HD % 64 == 0);
+constexpr int SPLIT_TILE = USE_TMA ? 32 : BN;    // the decode kernels' key tile: splits are whole tiles of it
 enum { GAVE_UP_DECODE = 21, GAVE_UP_PREFILL = 22 };
 
 // Byte offset of 16-byte chunk `chunk` of row `row` in a tile of ROWS rows.  cp.async layout: rows of
@@ -320,6 +321,15 @@ struct TileRing {
 constexpr int DEC_STAGES = 3;
 constexpr int DEC_SMEM = 1024 + 16 * ROWB + DEC_STAGES * 2 * TILE_BYTES + 64;
 
+// Keys per split of one request.  The launch fixes the number of splits (from the longest context it may see:
+// under a captured graph that is the reach of the block table); each request then cuts its own keys evenly
+// over them, in whole tiles and not below the planned size's floor of 128, so a request far shorter than
+// the bound still gives every split a share instead of filling the first and starving the rest.
+__device__ __forceinline__ int keys_per_split(int ctx, int split_keys, int max_splits, int tile) {
+    const int even = ((ctx + max_splits - 1) / max_splits + tile - 1) / tile * tile;
+    return max(min(split_keys, 128), even);
+}
+
 __global__ void __launch_bounds__(NTHREADS)
 decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
               const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
@@ -333,9 +343,10 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int num_splits = (ctx + split_keys - 1) / split_keys;
+    const int part_keys = keys_per_split(ctx, split_keys, max_splits, SPLIT_TILE);
+    const int num_splits = (ctx + part_keys - 1) / part_keys;
     if (split >= num_splits) return;
-    const int key_lo = max(split * split_keys, first), key_hi = min(ctx, (split + 1) * split_keys);
+    const int key_lo = max(split * part_keys, first), key_hi = min(ctx, (split + 1) * part_keys);
     const int rep = nq / nkv, token = req_q_start[r];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // stages at a 1024-byte boundary (swizzle atoms of the box copies), then the query tile, then barriers
@@ -431,6 +442,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
 // same warp: a parity wait tells only the current phase from the one before it, and a warp that saw
 // every second fill of a stage could take an old phase for the one it is waiting for.
 constexpr int WS_BN = 32;
+static_assert(!USE_TMA || SPLIT_TILE == WS_BN, "splits are whole tiles of the kernel that runs");
 constexpr int MERGE_MAX_SPLITS = 256;
 constexpr int WS_STAGES = 6;
 constexpr int WS_CONSUMERS = 6;
@@ -455,9 +467,10 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     if (req_q_len[r] != 1) return;
     const int ctx = req_ctx_len[r], pos = ctx - 1;
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    const int num_splits = (ctx + split_keys - 1) / split_keys;
+    const int part_keys = keys_per_split(ctx, split_keys, max_splits, SPLIT_TILE);
+    const int num_splits = (ctx + part_keys - 1) / part_keys;
     if (split >= num_splits) return;
-    const int key_lo = max(split * split_keys, first), key_hi = min(ctx, (split + 1) * split_keys);
+    const int key_lo = max(split * part_keys, first), key_hi = min(ctx, (split + 1) * part_keys);
     const int rep = nq / nkv, token = req_q_start[r];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -677,7 +690,8 @@ __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* 
     pdl_begin();
     const int head = blockIdx.x, r = blockIdx.y;
     if (req_q_len[r] != 1) return;
-    const int num_splits = (req_ctx_len[r] + split_keys - 1) / split_keys;
+    const int part_keys = keys_per_split(req_ctx_len[r], split_keys, max_splits, SPLIT_TILE);
+    const int num_splits = (req_ctx_len[r] + part_keys - 1) / part_keys;
     if (num_splits <= 1) return;
     const size_t slot0 = ((size_t)r * nq + head) * max_splits;
     if (threadIdx.x < 32) {
