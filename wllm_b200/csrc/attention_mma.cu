@@ -323,11 +323,12 @@ constexpr int DEC_SMEM = 1024 + 16 * ROWB + DEC_STAGES * 2 * TILE_BYTES + 64;
 
 // Keys per split of one request.  The launch fixes the number of splits (from the longest context it may see:
 // under a captured graph that is the reach of the block table); each request then cuts its own keys evenly
-// over them, in whole tiles and not below the planned size's floor of 128, so a request far shorter than
-// the bound still gives every split a share instead of filling the first and starving the rest.
+// over them, in whole tiles, so a request shorter than the bound still gives every split a share instead of
+// filling the first and starving the rest; but not in parts below 512 keys (or the planned size, if that is
+// smaller): a CTA's fixed cost is worth about that many.
 __device__ __forceinline__ int keys_per_split(int ctx, int split_keys, int max_splits, int tile) {
     const int even = ((ctx + max_splits - 1) / max_splits + tile - 1) / tile * tile;
-    return max(min(split_keys, 128), even);
+    return max(min(split_keys, 512), even);
 }
 
 __global__ void __launch_bounds__(NTHREADS)
