@@ -321,12 +321,18 @@ struct TileRing {
 constexpr int DEC_STAGES = 3;
 constexpr int DEC_SMEM = 1024 + 16 * ROWB + DEC_STAGES * 2 * TILE_BYTES + 64;
 
-// Keys per split of one request.  The launch fixes the number of splits (from the longest context it may see:
-// under a captured graph that is the reach of the block table); each request then cuts its own keys evenly
-// over them, in whole tiles, so a request shorter than the bound still gives every split a share instead of
-// filling the first and starving the rest; but not in parts below 512 keys (or the planned size, if that is
-// smaller): a CTA's fixed cost is worth about that many.
+// Keys per split of one request.  The launch fixes the number of splits and a planned size (from the longest
+// context it may see: under a captured graph that is the reach of the block table).  When the whole grid is
+// resident at once (at most one CTA an SM), each request cuts its own keys evenly over its splits, in whole
+// tiles, so that a request shorter than the bound does not fill its first split and starve the rest; but not
+// in parts below 512 keys (or the planned size, if that is smaller): a CTA's fixed cost is worth about that
+// many.  A grid of more CTAs than SMs keeps the planned size: the host chose it so that the short rests,
+// which start last, fill the second round.
+// (`split_keys` arrives negated when the grid is resident at once: the host knows, and the merge kernel, whose
+// grid differs, has to cut the same way.)
 __device__ __forceinline__ int keys_per_split(int ctx, int split_keys, int max_splits, int tile) {
+    if (split_keys > 0) return split_keys;
+    split_keys = -split_keys;
     const int even = ((ctx + max_splits - 1) / max_splits + tile - 1) / tile * tile;
     return max(min(split_keys, 512), even);
 }
@@ -939,6 +945,7 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     }
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)requests * nq * max_splits * HD;
+    if ((long long)requests * nkv * max_splits <= 148) split_keys = -split_keys;     // resident at once: cut evenly
     int st;
     if (USE_TMA) {
         // the last CTA of each (request, kv head) merges the splits itself where a counter is to be had
