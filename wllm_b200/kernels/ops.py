@@ -15,7 +15,7 @@ from __future__ import annotations
 import functools
 
 import ctypes
-from ctypes import c_float, c_int, c_void_p
+from ctypes import c_float, c_void_p
 
 import torch
 
