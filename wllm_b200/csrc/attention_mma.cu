@@ -10,10 +10,11 @@
 //            whole 32-key tiles in turn); other head sizes run four warps that take 16-key
 //            slices of every 64-key tile.  The warps merge at the end.  Splits of
 //            `split_keys` keys give a long context to many SMs; each writes its partial
-//            (max, sum, unnormalised output) to scratch, and they are merged in split order:
-//            by the CTA that finishes last (warp-specialised kernel, which counts arrivals
-//            per request and kv head) or by a second kernel.  A request with a single split
-//            writes its output directly.
+//            (max, sum, unnormalised output) to scratch and a second kernel merges them
+//            in split order.  A request with a single split writes its output directly.
+//            (Letting the CTA that finishes last merge them inside the kernel was built and
+//            measured: a gain of 1% at first, a loss of 4% once the kernels around it had
+//            become shorter; the merge kernel spreads over 64 CTAs what one CTA did alone.)
 //   prefill  one CTA per (request with several new tokens, kv head, tile of 128 rows),
 //            rows = (token, query head of the group).  Head sizes in steps of 64 run on
 //            tcgen05 (scores and output accumulate in tensor memory: attention_prefill_tc.cuh);
@@ -464,9 +465,8 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
                  const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                  const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                  int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                 int* __restrict__ arrivals, int* __restrict__ status) {
+                 int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
-    __shared__ int s_last;
     pdl_launch_dependents();
     // The step's index arrays were copied before its first kernel started, and no kernel of this step writes
     // a key below the new token's place: they may be read before this kernel waits for its predecessor.
@@ -626,63 +626,6 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
             *reinterpret_cast<float4*>(part_o + slot * HD + d) = O;
             if (d == 0) { part_ml[slot * 2] = sm_row[row * 2]; part_ml[slot * 2 + 1] = sm_row[row * 2 + 1]; }
         }
-    }
-    if (num_splits == 1 || arrivals == nullptr) return;
-    // The CTA that finishes last among the splits of this (request, kv head) merges them, with the arithmetic
-    // of merge_kernel, so that no second kernel has to wait for this one to drain.  Every thread publishes its
-    // partial results (fence), one thread counts the CTA in; the counter goes back to zero for the next launch.
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int before = atomicAdd(&arrivals[r * nkv + g], 1);
-        s_last = before == num_splits - 1;
-        if (s_last) arrivals[r * nkv + g] = 0;
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    float* sm_w = reinterpret_cast<float*>(smem);                   // [16][MERGE_MAX_SPLITS] weights of the splits
-    float* sm_inv = sm_w + 16 * MERGE_MAX_SPLITS;                   // [16] 1 / sum
-    for (int row = warp; row < rep; row += WS_THREADS / 32) {
-        const size_t slot0 = ((size_t)r * nq + g * rep + row) * max_splits;
-        float M = -INFINITY;
-        for (int sp = lane; sp < num_splits; sp += 32) M = fmaxf(M, __ldcg(part_ml + (slot0 + sp) * 2));
-        M = warp_max(M);
-        const float mbase = M == -INFINITY ? 0.f : M;
-        float L = 0.f;
-        for (int sp = lane; sp < num_splits; sp += 32) {
-            const float f = exp2f(__ldcg(part_ml + (slot0 + sp) * 2) - mbase);
-            sm_w[row * MERGE_MAX_SPLITS + sp] = f;
-            L += __ldcg(part_ml + (slot0 + sp) * 2 + 1) * f;
-        }
-        L = warp_sum(L);
-        if (lane == 0) sm_inv[row] = 1.0f / L;
-    }
-    __syncthreads();
-    // four output columns a thread; the loads of eight splits are issued together, the sums run in split order
-    for (int idx = threadIdx.x; idx < rep * (HD / 4); idx += WS_THREADS) {
-        const int row = idx / (HD / 4), d = (idx % (HD / 4)) * 4;
-        const size_t slot0 = ((size_t)r * nq + g * rep + row) * max_splits;
-        const float* w = sm_w + row * MERGE_MAX_SPLITS;
-        float O[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int sp = 0; sp < num_splits; sp += 8) {
-            float4 p[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                p[u] = sp + u < num_splits ? __ldcg(reinterpret_cast<const float4*>(part_o + (slot0 + sp + u) * HD + d))
-                                           : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (sp + u < num_splits) {
-                    const float f = w[sp + u];
-                    O[0] += p[u].x * f; O[1] += p[u].y * f; O[2] += p[u].z * f; O[3] += p[u].w * f;
-                }
-        }
-        const float inv = sm_inv[row];
-        __nv_bfloat162 lo = __floats2bfloat162_rn(O[0] * inv, O[1] * inv), hi = __floats2bfloat162_rn(O[2] * inv, O[3] * inv);
-        __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(out + (size_t)token * out_stride + (size_t)(g * rep + row) * HD + d);
-        dst[0] = lo;
-        dst[1] = hi;
     }
 }
 
@@ -870,13 +813,11 @@ static int pool_map(const void* ptr, long long rows, int box_rows, CUtensorMap* 
 
 WLLM_API int wllm_attention_mma_head_dim() { return HD; }
 
-// Arrival counters of the split-key decode kernel, one per (request, kv head); zero between launches (the
-// merging CTA resets its counter).  One set per device: launches that may overlap in time (two streams)
-// must not share it, and the engine has one stream.
+// Arrival counters of the prefill tiles that two CTAs share; zero between launches (the merging CTA resets
+// its counter).  One set per device: launches that may overlap in time (two streams) must not share it, and
+// the engine has one stream.
 constexpr int ARRIVAL_SLOTS = 1 << 16;
-constexpr int FUSED_MERGE_SPLITS = 32;     // more splits than this are merged by the second kernel, on many SMs
-static __device__ int g_arrivals[ARRIVAL_SLOTS];
-static __device__ int g_tile_arrivals[ARRIVAL_SLOTS];      // the same for the tiles that two prefill CTAs share
+static __device__ int g_tile_arrivals[ARRIVAL_SLOTS];
 template <typename Symbol>
 static int* symbol_address(const Symbol& symbol, int** cache) {
     int dev = -1;
@@ -887,10 +828,6 @@ static int* symbol_address(const Symbol& symbol, int** cache) {
         cache[dev] = static_cast<int*>(p);
     }
     return cache[dev];
-}
-static int* arrivals_address() {
-    static int* addr[64];
-    return symbol_address(g_arrivals, addr);
 }
 static int* tile_arrivals_address() {
     static int* addr[64];
@@ -947,16 +884,12 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     float* part_ml = scratch + (size_t)requests * nq * max_splits * HD;
     if ((long long)requests * nkv * max_splits <= 148) split_keys = -split_keys;     // resident at once: cut evenly
     int st;
-    if (USE_TMA) {
-        // the last CTA of each (request, kv head) merges the splits itself where a counter is to be had
-        int* arrivals = (long long)requests * nkv <= ARRIVAL_SLOTS && max_splits > 1 && max_splits <= FUSED_MERGE_SPLITS
-                            ? arrivals_address() : nullptr;
+    if (USE_TMA)
         st = wllm_launch(decode_ws_kernel, dim3(requests, nkv, max_splits), WS_THREADS, WS_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                          block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o,
-                         part_ml, arrivals, status);
-        if (arrivals != nullptr) return st;
-    } else
+                         part_ml, status);
+    else
         st = wllm_launch(decode_kernel, dim3(requests, nkv, max_splits), NTHREADS, DEC_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                          req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window,

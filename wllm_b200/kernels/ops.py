@@ -229,7 +229,7 @@ def attention_mma_decode(q, out, k_pages, v_pages, req_q_start, req_q_len, req_c
                                          _ptr(_status_word(q.device)), _stream()),
            f"attention_mma_decode(head_dim={hd}, heads={nq}/{nkv})")
     global launches
-    launches += 1 if max_splits > 1 and (hd % 64 != 0 or max_splits > 32) else 0    # the merge kernel, where it is not fused
+    launches += 1 if max_splits > 1 else 0    # the merge kernel
 
 
 def attention_prefill_halves_floats(requests: int, max_q_len: int, nq: int, nkv: int, hd: int) -> int:
