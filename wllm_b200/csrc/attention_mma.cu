@@ -659,10 +659,17 @@ __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* 
         if (threadIdx.x == 0) inv_l = 1.0f / L;
     }
     __syncthreads();
+    // the loads of sixteen splits are issued together (they do not depend on one another); the sums run in split order
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float O = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < num_splits; ++s) O += part_o[(slot0 + s) * HD + d] * w[s];
+        for (int s0 = 0; s0 < num_splits; s0 += 16) {
+            float p[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) p[u] = s0 + u < num_splits ? part_o[(slot0 + s0 + u) * HD + d] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+                if (s0 + u < num_splits) O += p[u] * w[s0 + u];
+        }
         out[(size_t)req_q_start[r] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O * inv_l);
     }
 }
