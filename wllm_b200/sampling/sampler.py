@@ -40,6 +40,8 @@ class Sampler:
         self._dev = self._out = None
         self._out_hosts = [None, None]   # two pinned result buffers: one is read while the next step fills the other
         self._turn = 0
+        self._side = None                # the results travel to the host on a stream of their own
+        self._read = None                # behind the last copy out of `_out`: the next launch overwrites it
         self._stats = None               # per-chunk (max, arg-max, sum) of the greedy path
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -56,14 +58,25 @@ class Sampler:
         rows = logits.shape[0]
         if rows == 0:
             return PendingSample(0, None, None, None)
+        main = torch.cuda.current_stream(self.device)
+        if self._read is not None:
+            main.wait_event(self._read)          # the copy out of the previous results is done (it has long been)
         tokens = self.launch(logits, params, counters, seeds, generated)
         self._turn ^= 1
         host = self._out_hosts[self._turn]
         if host is None or host.numel() < 2 * rows:
             host = self._out_hosts[self._turn] = torch.empty(max(2 * rows, 1024), dtype=torch.int32).pin_memory()
-        host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.device)
+        sampled = torch.cuda.Event()
+        sampled.record(main)
+        # the copy to the host leaves the step's stream free for the next step's first kernels
+        self._side.wait_event(sampled)
+        with torch.cuda.stream(self._side):
+            host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(self._side)
+        self._read = event
         self.d2h_bytes = 8 * rows
         return PendingSample(rows, tokens, host, event)
 
