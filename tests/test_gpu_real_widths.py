@@ -82,3 +82,25 @@ def test_bfloat16_matches_plain_under_every_cut(model):
         for k in ref:     # and the ranking of the top token survives, or is a near-tie
             top = int(ref[k].argmax())
             assert float(ref[k][top] - ref[k][int(rows[k].argmax())]) < 0.03 * max(1.0, scale), (name, cut, k)
+
+
+def test_steps_queued_back_to_back_see_their_own_index_arrays(model):
+    """Whole prompts stepped one after the other with no synchronisation in between and their logits dropped
+    at once: the host builds and sends the next step's index arrays while the step before still runs, and a
+    tensor freed on the host is still in use on the device.  The last step's logits are what a lone step gives.
+    (A staging buffer that the copy stream wrote too early once showed here as an illegal address.)"""
+    from test_gpu_replay import gpu_runner
+    from wllm_b200.engine import StepEntry
+    name, folder, reqs, ref = model
+    runner = gpu_runner(folder, torch.bfloat16, 16, 64)
+    for i in range(6):
+        rc = runner.cache.open(f"warm{i}")
+        runner.step([StepEntry(rc, reqs["a"], [len(reqs["a"]) - 1])])       # result dropped, nothing waited for
+        runner.cache.close(rc)
+    rc = runner.cache.open("last")
+    got = runner.step([StepEntry(rc, reqs["b"], [69])])[0].float().cpu()
+    lone = gpu_runner(folder, torch.bfloat16, 16, 64)
+    want = lone.step([StepEntry(lone.cache.open("x"), reqs["b"], [69])])[0].float().cpu()
+    assert torch.equal(got, want)
+    scale = max(float(r.abs().max()) for r in ref.values())
+    assert float((got.double() - ref[("b", 69)].double()).abs().max()) < 0.03 * max(1.0, scale)

@@ -46,11 +46,17 @@ class PinnedRing:
         buf[:n].copy_(torch.from_numpy(host))
         if self._side is None:
             self._side = torch.cuda.Stream(self.device)
+        main, side = torch.cuda.current_stream(self.device), self._side
         staged = self._staged[i]
         if staged is None or staged.numel() < n:
-            staged = self._staged[i] = torch.empty(max(n, 4096), dtype=torch.int32, device=self.device)
+            # Allocated under the copy stream: a block that the allocator hands out under the step's stream may
+            # still be in use by kernels queued there (a tensor freed on the host while its step runs), which is
+            # in order for work on that stream and a race for a copy on another one.
+            with torch.cuda.stream(side):
+                staged = torch.empty(max(n, 4096), dtype=torch.int32, device=self.device)
+            staged.record_stream(main)
+            self._staged[i] = staged
             self._consumed[i] = None
-        main, side = torch.cuda.current_stream(self.device), self._side
         if self._consumed[i] is not None:
             side.wait_event(self._consumed[i])          # the staging buffer's last reader is done
         with torch.cuda.stream(side):
