@@ -7,7 +7,7 @@ where a repetition penalty applies.
 """
 from __future__ import annotations
 
-from ctypes import c_void_p
+from ctypes import byref, c_int, c_void_p
 
 import numpy as np
 import torch
@@ -42,7 +42,7 @@ class Sampler:
         self._turn = 0
         self._side = None                # the results travel to the host on a stream of their own
         self._read = None                # behind the last copy out of `_out`: the next launch overwrites it
-        self._stats = None               # per-chunk (max, arg-max, sum) of the greedy path
+        self._scratch = None             # per-row state, chunk statistics and histograms; zero before first use
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -80,17 +80,21 @@ class Sampler:
         self.d2h_bytes = 8 * rows
         return PendingSample(rows, tokens, host, event)
 
+    def _scratch_for(self, rows: int, lib) -> c_void_p:
+        need = int(lib.wllm_sample_scratch_row_bytes()) * max(rows, 64)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.zeros(need, dtype=torch.uint8, device=self.device)
+        return c_void_p(self._scratch.data_ptr())
+
     def _launch_greedy(self, logits: torch.Tensor) -> torch.Tensor:
-        """All rows greedy and unpenalised: no options to send; arg-max and log-sum-exp by 32 blocks a row."""
+        """All rows greedy and unpenalised: no options to send, and the first pass alone."""
         rows, V = logits.shape
         if self._out is None or self._out.numel() < 2 * rows:
             self._out = torch.empty(max(2 * rows, 1024), dtype=torch.int32, device=self.device)
-        if self._stats is None or self._stats.numel() < rows * 96:
-            self._stats = torch.empty(max(rows, 64) * 96, dtype=torch.float32, device=self.device)
         lib = load_family("sampling")
-        ops._check(lib.wllm_sample_greedy(c_void_p(logits.data_ptr()), logits.stride(0), rows, V,
-                                          c_void_p(self._stats.data_ptr()), c_void_p(self._out.data_ptr()),
-                                          c_void_p(self._out.data_ptr() + 4 * rows), ops._stream()), "sample_greedy")
+        ops._check(lib.wllm_sample_greedy(c_void_p(logits.data_ptr()), logits.stride(0), rows, V, self._scratch_for(rows, lib),
+                                          c_void_p(self._out.data_ptr()), c_void_p(self._out.data_ptr() + 4 * rows),
+                                          ops._stream()), "sample_greedy")
         ops.launches += 1
         self.h2d_bytes = 0
         return self._out[:rows]
@@ -125,15 +129,21 @@ class Sampler:
             self._dev = torch.empty(max(total, 8192), dtype=torch.int32, device=self.device)
         if self._out is None or self._out.numel() < 2 * rows:
             self._out = torch.empty(max(2 * rows, 1024), dtype=torch.int32, device=self.device)
+        lib = load_family("sampling")
+        scratch = self._scratch_for(rows, lib)
+        filters = (1 if any(p.temperature != 0.0 and (p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0) for p in params) else 0) | \
+                  (2 if any(p.temperature != 0.0 and (p.top_k > 0 or p.top_p < 1.0) for p in params) else 0)
         self._ring.send(host, self._dev)
         base = self._dev.data_ptr()
 
         def at(i):
             return c_void_p(base + 4 * i)
-        lib = load_family("sampling")
+        launched = c_int(0)
         ops._check(lib.wllm_sample(c_void_p(logits.data_ptr()), logits.stride(0), rows, V, at(0), at(rows), at(2 * rows),
                                    at(3 * rows), at(4 * rows), at(5 * rows), at(6 * rows), at(7 * rows), at(8 * rows),
-                                   at(9 * rows + 1), c_void_p(self._out.data_ptr()),
-                                   c_void_p(self._out.data_ptr() + 4 * rows), ops._stream()), "sample")
+                                   at(9 * rows + 1), scratch, filters,
+                                   c_void_p(self._out.data_ptr()), c_void_p(self._out.data_ptr() + 4 * rows),
+                                   byref(launched), ops._stream()), "sample")
+        ops.launches += launched.value
         self.h2d_bytes = total * 4
         return self._out[:rows]
