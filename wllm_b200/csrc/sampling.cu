@@ -111,9 +111,28 @@ __device__ __forceinline__ unsigned key_of(float x) {
     const unsigned b = __float_as_uint(x);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
-// exp(s - s_max) of s = x / T, and the same in 40-bit fixed point
-__device__ __forceinline__ float weight_of(float x, float xmax, float inv_t) { return expf((x - xmax) * inv_t); }
+// exp(s - s_max) of s = x / T, as 2^((x - x_max) * log2(e) / T) by the hardware's exponential (relative error
+// 2^-22: every pass uses this one function, so they agree with one another exactly), and the same in 40-bit
+// fixed point
+__device__ __forceinline__ float weight_of(float x, float xmax, float inv_t) {
+    const float c = inv_t * 1.4426950408889634f;
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmaf(x, c, -(xmax * c))));
+    return y;
+}
 __device__ __forceinline__ u64 mass_of(float x, float xmax, float inv_t) { return __float2ull_rd(weight_of(x, xmax, inv_t) * MASS_ONE); }
+
+// The float whose key is `key`, and bounds lo <= x <= hi that hold for every x whose key lies in
+// [first, last] (they may hold for a few more: -0 and +0 compare equal but have different keys).
+__device__ __forceinline__ float float_of_key(unsigned key) {
+    return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+__device__ __forceinline__ void bounds_of_keys(unsigned first, unsigned last, float& lo, float& hi) {
+    lo = float_of_key(first);
+    hi = float_of_key(last);
+    if (lo != lo) lo = -INFINITY;     // the ends of the key range are not-a-number patterns
+    if (hi != hi) hi = INFINITY;
+}
 
 __device__ __forceinline__ unsigned uniform_bits(unsigned long long seed, unsigned long long counter) {
     unsigned long long z = seed + 0x9E3779B97F4A7C15ull * (counter + 1ull);
@@ -319,13 +338,16 @@ template <int LEVEL>
 __global__ void __launch_bounds__(ST)
 sample_select_kernel(const float* __restrict__ logits, int row_stride, int V, unsigned char* __restrict__ scratch,
                      const float* __restrict__ top_p, const float* __restrict__ min_p) {
-    // A bin's mass is held as two 32-bit halves: shared memory adds 32-bit integers in one instruction.
-    __shared__ unsigned hc[BINS], hm_lo[BINS], hm_hi[BINS];
+    // Pass 0 sees every value, most of them in a few bins: it counts in shared memory first.  A bin's mass is
+    // held there as two 32-bit halves, which shared memory adds in one instruction.  The later passes see
+    // the few values that share the digits found so far and add them to the row's histogram directly.
+    constexpr int LOCAL = LEVEL == 0 ? BINS : 4;
+    __shared__ __align__(16) unsigned hc[LOCAL], hm_lo[LOCAL], hm_hi[LOCAL];
     __shared__ u64 warp_totals[WARPS];
     __shared__ unsigned us[32];
     __shared__ int flag;
     pdl_begin();
-    const int chunk = blockIdx.x, chunks = gridDim.x, row = blockIdx.y, tid = threadIdx.x;
+    const int chunk = blockIdx.x, chunks = gridDim.x, row = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
     const RowScratch rs = row_scratch(scratch, row);
     RowState* s = rs.state;
     const unsigned searching = s->searching;
@@ -337,33 +359,72 @@ sample_select_kernel(const float* __restrict__ logits, int row_stride, int V, un
     const float inv_t = s->inv_t, xmax = s->xmax;
     const unsigned above_k = above_of<LEVEL>(s->prefix_k), above_p = above_of<LEVEL>(s->prefix_p);
     const float p_min = min_p[row];
-
-    for (int b = tid; b < BINS; b += ST) { hc[b] = 0u; hm_lo[b] = 0u; hm_hi[b] = 0u; }
-    __syncthreads();
-    unsigned lowest = 0xffffffffu;
-    for_each_of_chunk(x, lo, hi, row_is_aligned(x), [&](int, float v) {
-        const unsigned key = key_of(v);
-        const unsigned d = digit_of<LEVEL>(key), a = above_of<LEVEL>(key);
-        if (do_k && a == above_k) atomicAdd(&hc[d], 1u);
-        if (do_p && a == above_p) {
-            const u64 m = mass_of(v, xmax, inv_t);
-            const unsigned ml = (unsigned)m, mh = (unsigned)(m >> 32);
-            if (ml) {
-                const unsigned old = atomicAdd(&hm_lo[d], ml);
-                if (old + ml < old) atomicAdd(&hm_hi[d], 1u);      // this addition wrapped the lower half
-            }
-            if (mh) atomicAdd(&hm_hi[d], mh);
-        }
-        // p_i < min_p * p_max is dropped  <=>  exp(s_i - s_max) < min_p; the keys are monotone in s
-        if (do_min && !(weight_of(v, xmax, inv_t) < p_min)) lowest = min(lowest, key);
-    });
-    __syncthreads();
     unsigned* gc = rs.counts + LEVEL * BINS;
     u64* gm = rs.masses + LEVEL * BINS;
-    for (int b = tid; b < BINS; b += ST) {
-        if (hc[b]) atomicAdd(gc + b, hc[b]);
-        const u64 m = ((u64)hm_hi[b] << 32) | hm_lo[b];
-        if (m) atomicAdd(gm + b, m);
+    unsigned lowest = 0xffffffffu;
+
+    if (LEVEL == 0) {
+        for (int b = tid * 4; b < BINS; b += ST * 4) {
+            *reinterpret_cast<uint4*>(hc + b) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(hm_lo + b) = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(hm_hi + b) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncthreads();
+        for_each_of_chunk(x, lo, hi, row_is_aligned(x), [&](int, float v) {
+            const unsigned key = key_of(v);
+            const unsigned d = digit_of<LEVEL>(key);
+            if (do_k) atomicAdd(&hc[d], 1u);
+            if (do_p || do_min) {
+                const float w = weight_of(v, xmax, inv_t);
+                if (do_p) {
+                    const u64 m = __float2ull_rd(w * MASS_ONE);
+                    const unsigned ml = (unsigned)m, mh = (unsigned)(m >> 32);
+                    if (ml) {
+                        const unsigned old = atomicAdd(&hm_lo[d], ml);
+                        if (old + ml < old) atomicAdd(&hm_hi[d], 1u);      // this addition wrapped the lower half
+                    }
+                    if (mh) atomicAdd(&hm_hi[d], mh);
+                }
+                // p_i < min_p * p_max is dropped  <=>  exp(s_i - s_max) < min_p; the keys are monotone in s
+                if (do_min && !(w < p_min)) lowest = min(lowest, key);
+            }
+        });
+        __syncthreads();
+        for (int b = tid * 4; b < BINS; b += ST * 4) {
+            const uint4 c4 = *reinterpret_cast<const uint4*>(hc + b);
+            const uint4 l4 = *reinterpret_cast<const uint4*>(hm_lo + b), h4 = *reinterpret_cast<const uint4*>(hm_hi + b);
+            const unsigned cs[4] = {c4.x, c4.y, c4.z, c4.w}, ls[4] = {l4.x, l4.y, l4.z, l4.w}, hs[4] = {h4.x, h4.y, h4.z, h4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (cs[j]) atomicAdd(gc + b + j, cs[j]);
+                const u64 m = ((u64)hs[j] << 32) | ls[j];
+                if (m) atomicAdd(gm + b + j, m);
+            }
+        }
+    } else {
+        // Values outside the bins found so far fail two comparisons of floats and cost nothing more.
+        constexpr unsigned width = LEVEL == 1 ? (1u << 21) : (1u << 10);
+        float k_lo, k_hi, p_lo, p_hi;
+        bounds_of_keys(place<LEVEL - 1>(above_k) , place<LEVEL - 1>(above_k) + (width - 1u), k_lo, k_hi);
+        bounds_of_keys(place<LEVEL - 1>(above_p), place<LEVEL - 1>(above_p) + (width - 1u), p_lo, p_hi);
+        for_each_of_chunk(x, lo, hi, row_is_aligned(x), [&](int, float v) {
+            const bool near_k = do_k && v >= k_lo && v <= k_hi, near_p = do_p && v >= p_lo && v <= p_hi;
+            if (near_k || near_p) {
+                const unsigned key = key_of(v);
+                const unsigned d = digit_of<LEVEL>(key), a = above_of<LEVEL>(key);
+                if (near_k && a == above_k) {       // one addition for the lanes of a warp that meet in a bin
+                    const unsigned peers = __match_any_sync(__activemask(), d);
+                    if (lane == __ffs(peers) - 1) atomicAdd(gc + d, (unsigned)__popc(peers));
+                }
+                if (near_p && a == above_p) {
+                    const u64 m = mass_of(v, xmax, inv_t);
+                    const unsigned peers = __match_any_sync(__activemask(), d);
+                    u64 sum = 0;
+                    for (unsigned rest = peers; rest; rest &= rest - 1) sum += __shfl_sync(peers, m, __ffs(rest) - 1);
+                    if (lane == __ffs(peers) - 1 && sum) atomicAdd(gm + d, sum);
+                }
+            }
+        });
     }
     if (do_min) {
 #pragma unroll

@@ -5,6 +5,7 @@ print what it achieved against the roofline.  The same command under `ncu` gives
     python -m wllm_b200.kernels.cases gemm --m 8 --n 2048 --k 16384 --split
     python -m wllm_b200.kernels.cases attention-decode --requests 16 --context 8192
     python -m wllm_b200.kernels.cases attention-prefill --requests 1 --tokens 2048 --context 2048
+    python -m wllm_b200.kernels.cases sampling --rows 8 --vocab 256000 --top-k 50 --top-p 0.9
 
 Operands are larger than L2 where the case is bound by memory (several weight copies are cycled), so the
 figures are DRAM figures.  Peaks: MEASURED_PEAKS.json at the repository root when present, else the fallback
@@ -120,6 +121,30 @@ def attention(args, decode: bool) -> None:
           f"{flops / ms / 1e9:.1f} TFLOP/s ({flops / ms / 1e9 / tf:.3f} of {src} {tf:.0f}), status {ops.tc_gemm_status(DEV)}")
 
 
+def sampling(args) -> None:
+    """The sampling passes on rows of logits that lie in L2 (as the head's product leaves them), options on the device."""
+    from ..sampling import SamplingParams
+    from ..sampling.sampler import Sampler
+    rows, V = args.rows, args.vocab
+    sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p, seed=1)
+    sampler = Sampler(DEV)
+    logits = torch.randn(rows, V, device=DEV) * 3.0
+    logits[:, 77] += 8.0                                        # a peaked row, as a model's is
+    lists = ([sp] * rows, [3] * rows, [7] * rows, [set()] * rows)
+    sampler.launch(logits, *lists)                              # sends the options once
+    greedy = args.temperature == 0.0
+    if greedy:
+        ms = timed(lambda: sampler.launch(logits, *lists), args.iters)
+    else:
+        from ..sampling.sampler import pack_options
+        filters = pack_options(*lists)[1]
+        ms = timed(lambda: sampler.launch_packed(logits, filters), args.iters)
+    passes = 1 if greedy else 2 + (1 if filters & 1 else 0) + (2 if filters & 2 else 0)
+    print(f"sampling rows={rows} vocab={V} temperature={args.temperature} top_k={args.top_k} top_p={args.top_p} "
+          f"min_p={args.min_p}: {ms * 1e3:.1f} us, {passes} passes over {rows * V * 4 / 1e6:.1f} MB of logits "
+          f"({passes * rows * V * 4 / ms / 1e6:.0f} GB/s out of L2)")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m wllm_b200.kernels.cases", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -139,6 +164,13 @@ def main(argv=None) -> int:
         a.add_argument("--head-dim", type=int, default=256)
         a.add_argument("--page-size", type=int, default=64)
         a.add_argument("--no-share", action="store_true", help="prefill: never share a heavy tile between two CTAs")
+    sm = sub.add_parser("sampling")
+    sm.add_argument("--rows", type=int, default=8)
+    sm.add_argument("--vocab", type=int, default=256000)
+    sm.add_argument("--temperature", type=float, default=0.8)
+    sm.add_argument("--top-k", type=int, default=0)
+    sm.add_argument("--top-p", type=float, default=1.0)
+    sm.add_argument("--min-p", type=float, default=0.0)
     for p in sub.choices.values():
         p.add_argument("--iters", type=int, default=10)
     args = ap.parse_args(argv)
@@ -147,6 +179,8 @@ def main(argv=None) -> int:
         return 1
     if args.case == "gemm":
         gemm(args)
+    elif args.case == "sampling":
+        sampling(args)
     else:
         attention(args, decode=args.case == "attention-decode")
     return 0

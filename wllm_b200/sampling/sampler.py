@@ -106,34 +106,20 @@ class Sampler:
             raise ops.KernelError("sampling needs float32 logits with unit stride along the vocabulary")
         if all(p.temperature == 0.0 and p.repetition_penalty == 1.0 for p in params):
             return self._launch_greedy(logits)
-        gen_lists = [sorted(g) if p.repetition_penalty != 1.0 else [] for p, g in zip(params, generated)]
-        offsets = np.zeros(rows + 1, dtype=np.int32)
-        offsets[1:] = np.cumsum([len(g) for g in gen_lists])
-        n_gen = int(offsets[-1])
-        total = 8 * rows + (rows + 1) + n_gen
-        host = np.zeros(total, dtype=np.int32)
-        f = host.view(np.float32)
-        f[0:rows] = [p.temperature for p in params]
-        host[rows:2 * rows] = [p.top_k for p in params]
-        f[2 * rows:3 * rows] = [p.top_p for p in params]
-        f[3 * rows:4 * rows] = [p.min_p for p in params]
-        f[4 * rows:5 * rows] = [p.repetition_penalty for p in params]
-        s = np.asarray([x & 0xFFFFFFFFFFFFFFFF for x in seeds], dtype=np.uint64)
-        host[5 * rows:6 * rows] = (s & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)
-        host[6 * rows:7 * rows] = (s >> np.uint64(32)).astype(np.uint32).view(np.int32)
-        host[7 * rows:8 * rows] = counters
-        host[8 * rows:9 * rows + 1] = offsets
-        if n_gen:
-            host[9 * rows + 1:] = np.concatenate([np.asarray(g, dtype=np.int32) for g in gen_lists if g])
-        if self._dev is None or self._dev.numel() < total:
-            self._dev = torch.empty(max(total, 8192), dtype=torch.int32, device=self.device)
+        host, filters = pack_options(params, counters, seeds, generated)
+        if self._dev is None or self._dev.numel() < host.shape[0]:
+            self._dev = torch.empty(max(host.shape[0], 8192), dtype=torch.int32, device=self.device)
+        self._ring.send(host, self._dev)
+        self.h2d_bytes = host.shape[0] * 4
+        return self.launch_packed(logits, filters)
+
+    def launch_packed(self, logits: torch.Tensor, filters: int) -> torch.Tensor:
+        """The kernels alone, on the options that the last `launch` left on the device."""
+        rows, V = logits.shape
         if self._out is None or self._out.numel() < 2 * rows:
             self._out = torch.empty(max(2 * rows, 1024), dtype=torch.int32, device=self.device)
         lib = load_family("sampling")
         scratch = self._scratch_for(rows, lib)
-        filters = (1 if any(p.temperature != 0.0 and (p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0) for p in params) else 0) | \
-                  (2 if any(p.temperature != 0.0 and (p.top_k > 0 or p.top_p < 1.0) for p in params) else 0)
-        self._ring.send(host, self._dev)
         base = self._dev.data_ptr()
 
         def at(i):
@@ -145,5 +131,33 @@ class Sampler:
                                    c_void_p(self._out.data_ptr()), c_void_p(self._out.data_ptr() + 4 * rows),
                                    byref(launched), ops._stream()), "sample")
         ops.launches += launched.value
-        self.h2d_bytes = total * 4
         return self._out[:rows]
+
+
+def pack_options(params: list, counters: list, seeds: list, generated: list):
+    """One int32 array with, row by row in this order: temperature, top-k, top-p, min-p, penalty, the seed's
+    lower and upper half, the counter, the offsets of each row's generated ids, and those ids; and which
+    selection passes some row needs (bit 0: any filter, bit 1: top-k or top-p)."""
+    rows = len(params)
+    gen_lists = [sorted(g) if p.repetition_penalty != 1.0 else [] for p, g in zip(params, generated)]
+    offsets = np.zeros(rows + 1, dtype=np.int32)
+    offsets[1:] = np.cumsum([len(g) for g in gen_lists])
+    n_gen = int(offsets[-1])
+    host = np.zeros(8 * rows + (rows + 1) + n_gen, dtype=np.int32)
+    f = host.view(np.float32)
+    f[0:rows] = [p.temperature for p in params]
+    host[rows:2 * rows] = [p.top_k for p in params]
+    f[2 * rows:3 * rows] = [p.top_p for p in params]
+    f[3 * rows:4 * rows] = [p.min_p for p in params]
+    f[4 * rows:5 * rows] = [p.repetition_penalty for p in params]
+    s = np.asarray([x & 0xFFFFFFFFFFFFFFFF for x in seeds], dtype=np.uint64)
+    host[5 * rows:6 * rows] = (s & np.uint64(0xFFFFFFFF)).astype(np.uint32).view(np.int32)
+    host[6 * rows:7 * rows] = (s >> np.uint64(32)).astype(np.uint32).view(np.int32)
+    host[7 * rows:8 * rows] = counters
+    host[8 * rows:9 * rows + 1] = offsets
+    if n_gen:
+        host[9 * rows + 1:] = np.concatenate([np.asarray(g, dtype=np.int32) for g in gen_lists if g])
+    sampled = [p for p in params if p.temperature != 0.0]
+    filters = (1 if any(p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0 for p in sampled) else 0) | \
+              (2 if any(p.top_k > 0 or p.top_p < 1.0 for p in sampled) else 0)
+    return host, filters
