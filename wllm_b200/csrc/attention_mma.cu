@@ -453,6 +453,7 @@ constexpr int WS_BN = 32;
 static_assert(!USE_TMA || SPLIT_TILE == WS_BN, "splits are whole tiles of the kernel that runs");
 constexpr int MERGE_MAX_SPLITS = 256;
 constexpr int WS_STAGES = 6;
+constexpr int WS_PAGE_IDS = 256;        // page numbers of a split kept in shared memory (16,384 keys of 64 a page)
 constexpr int WS_CONSUMERS = 6;
 static_assert(WS_STAGES % WS_CONSUMERS == 0, "every stage must belong to one consumer warp");
 constexpr int WS_TILE_BYTES = WS_BN * ROWB;
@@ -465,7 +466,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
                  const int* __restrict__ req_q_start, const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len,
                  const int* __restrict__ block_table, int max_pages, int nq, int nkv, int page_size, int window, float scale2,
                  int split_keys, int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                 int* __restrict__ status) {
+                 int whole_rows, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     pdl_launch_dependents();
     // The step's index arrays were copied before its first kernel started, and no kernel of this step writes
@@ -489,19 +490,28 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     const int t0 = key_lo / WS_BN, t1 = key_lo >= key_hi ? t0 : (key_hi + WS_BN - 1) / WS_BN;
     const int box_rows = page_size < WS_BN ? page_size : WS_BN;
 
-    // one tile of keys and values into stage s (the producer lane calls this)
+    __shared__ int page_ids[WS_PAGE_IDS];
+    const int page_lo = (t0 * WS_BN) >> page_shift, page_hi = t1 > t0 ? ((t1 * WS_BN - 1) >> page_shift) + 1 : page_lo;
+
+    // one tile of keys and values into stage s (the producer lane calls this); a step reads them once
+    const uint64_t stream = l2_evict_first();
     auto load_tile = [&](int t, int s) {
         const uint32_t k_dst = base + (2 * s) * WS_TILE_BYTES, v_dst = k_dst + WS_TILE_BYTES, bar = full0 + 8 * s;
         mbar_expect_tx(bar, 2 * WS_TILE_BYTES);
         for (int r0 = 0; r0 < WS_BN; r0 += box_rows) {
             const int key = t * WS_BN + r0, index = key >> page_shift;
-            int page = index < max_pages ? table[index] : 0;
+            int page = index - page_lo < WS_PAGE_IDS ? page_ids[index - page_lo] : (index < max_pages ? table[index] : 0);
             if (page < 0) page = 0;
             const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
+            if (whole_rows) {          // one box a tile: the maps have the column blocks as a third dimension
+                tma_load_3d_hint(k_dst, &k_map, bar, 0, row, 0, stream);
+                tma_load_3d_hint(v_dst, &v_map, bar, 0, row, 0, stream);
+                continue;
+            }
 #pragma unroll
             for (int cb = 0; cb < HD / 64; ++cb) {
-                tma_load_2d(k_dst + cb * (WS_BN * 128) + r0 * 128, &k_map, bar, cb * 64, row);
-                tma_load_2d(v_dst + cb * (WS_BN * 128) + r0 * 128, &v_map, bar, cb * 64, row);
+                tma_load_2d_hint(k_dst + cb * (WS_BN * 128) + r0 * 128, &k_map, bar, cb * 64, row, stream);
+                tma_load_2d_hint(v_dst + cb * (WS_BN * 128) + r0 * 128, &v_map, bar, cb * 64, row, stream);
             }
         }
     };
@@ -511,6 +521,10 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // The page numbers of this split come in with one round of loads by all threads, so that no tile's copy
+    // waits for a load of its own in the producer lane.
+    for (int i = threadIdx.x; i < min(WS_PAGE_IDS, page_hi - page_lo); i += WS_THREADS)
+        page_ids[i] = page_lo + i < max_pages ? table[page_lo + i] : 0;
     __syncthreads();
     // Tiles that end below the new token's place hold only keys of earlier steps: the first stages are
     // requested now, while the kernel that writes the new key and value (and the query) still runs.
@@ -785,30 +799,32 @@ static EncodeTiled encoder() {
     return fn;
 }
 struct PoolKey {
-    const void* ptr; long long rows; int box_rows;
-    bool operator==(const PoolKey& o) const { return ptr == o.ptr && rows == o.rows && box_rows == o.box_rows; }
+    const void* ptr; long long rows; int box_rows; bool whole_rows;
+    bool operator==(const PoolKey& o) const { return ptr == o.ptr && rows == o.rows && box_rows == o.box_rows && whole_rows == o.whole_rows; }
 };
 struct PoolKeyHash {
-    size_t operator()(const PoolKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)(k.rows * 31 + k.box_rows); }
+    size_t operator()(const PoolKey& k) const { return std::hash<const void*>()(k.ptr) ^ (size_t)(k.rows * 31 + k.box_rows * 2 + (k.whole_rows ? 1 : 0)); }
 };
 static std::unordered_map<PoolKey, CUtensorMap, PoolKeyHash> g_pool_maps;
 static std::mutex g_pool_mutex;
 
 // A pool [pages][nkv][page_size][HD] as a matrix of rows x HD; boxes of box_rows x 64 columns, 128-byte swizzle.
-static int pool_map(const void* ptr, long long rows, int box_rows, CUtensorMap* out) {
+// `whole_rows`: the columns as a third dimension of HD / 64 blocks of 64, so that one box holds whole rows and
+// arrives as [block][row][64 columns], the same place that HD / 64 boxes of the flat matrix fill one by one.
+static int pool_map(const void* ptr, long long rows, int box_rows, CUtensorMap* out, bool whole_rows = false) {
     if (!USE_TMA) { memset(out, 0, sizeof(*out)); return WLLM_OK; }
     std::lock_guard<std::mutex> lock(g_pool_mutex);
-    const PoolKey key{ptr, rows, box_rows};
+    const PoolKey key{ptr, rows, box_rows, whole_rows};
     auto it = g_pool_maps.find(key);
     if (it != g_pool_maps.end()) { *out = it->second; return WLLM_OK; }
     EncodeTiled enc = encoder();
     if (!enc) return 6;
-    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
+    const cuuint64_t dims[3] = {whole_rows ? 64u : (cuuint64_t)HD, (cuuint64_t)rows, (cuuint64_t)HD / 64};
+    const cuuint64_t strides[2] = {(cuuint64_t)HD * 2, 128};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)HD / 64};
+    const cuuint32_t elem[3] = {1, 1, 1};
     CUtensorMap m;
-    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+    const CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, whole_rows ? 3 : 2, const_cast<void*>(ptr), dims, strides, box, elem,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return 2000 + (int)r;
@@ -875,9 +891,10 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
     CUtensorMap km, vm;
     const long long rows = pool_pages * nkv * page_size;
     const int box_rows = USE_TMA ? (page_size < WS_BN ? page_size : WS_BN) : (page_size < BN ? page_size : BN);
-    int r = pool_map(k_pages, rows, box_rows, &km);
+    const bool whole_rows = USE_TMA && box_rows == WS_BN;      // pages of at least a tile's keys: one copy a tile
+    int r = pool_map(k_pages, rows, box_rows, &km, whole_rows);
     if (r) return r;
-    r = pool_map(v_pages, rows, box_rows, &vm);
+    r = pool_map(v_pages, rows, box_rows, &vm, whole_rows);
     if (r) return r;
     static bool configured = false;
     if (!configured) {
@@ -895,7 +912,7 @@ WLLM_API int wllm_attention_mma_decode(const void* q, int q_stride, void* out, i
         st = wllm_launch(decode_ws_kernel, dim3(requests, nkv, max_splits), WS_THREADS, WS_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                          block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, split_keys, max_splits, part_o,
-                         part_ml, status);
+                         part_ml, whole_rows ? 1 : 0, status);
     else
         st = wllm_launch(decode_kernel, dim3(requests, nkv, max_splits), NTHREADS, DEC_SMEM, stream,
                          (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,

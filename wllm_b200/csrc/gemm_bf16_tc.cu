@@ -173,6 +173,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            // With one tile of rows every weight is read once in this launch: its lines go first when the L2
+            // needs room.  With more tiles of rows the L2 serves the weights to the later ones.
+            const bool once = tiles_m == 1;
+            const uint64_t stream = l2_evict_first();
+            auto load_w = [&](uint32_t dst, uint32_t bar, int x, int y) {
+                if (once) tma_load_2d_hint(dst, &map_w, bar, x, y, stream);
+                else tma_load_2d(dst, &map_w, bar, x, y);
+            };
             // The weights are written by no kernel of the step: the first stages' W tiles are requested before
             // this kernel waits for its predecessor, so they stream while that kernel still runs.  A (the
             // activations the predecessor wrote) follows after the wait.
@@ -186,8 +194,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int i = 0; i < early; ++i) {
                     const uint32_t b_dst = ring + i * STAGE_BYTES + A_BYTES, bar = full0 + 8 * i;
                     mbar_expect_tx(bar, STAGE_BYTES);
-                    tma_load_2d(b_dst, &map_w, bar, (kb_lo + i) * BK, n0);
-                    tma_load_2d(b_dst + B_HALF, &map_w, bar, (kb_lo + i) * BK, GATED ? up_row_offset + n0 : n0 + half_rows);
+                    load_w(b_dst, bar, (kb_lo + i) * BK, n0);
+                    load_w(b_dst + B_HALF, bar, (kb_lo + i) * BK, GATED ? up_row_offset + n0 : n0 + half_rows);
                 }
             }
             pdl_wait();
@@ -204,8 +212,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
                         mbar_expect_tx(bar, STAGE_BYTES);
                         tma_load_2d(a_dst, &map_a, bar, kb * BK, m0);
-                        tma_load_2d(b_dst, &map_w, bar, kb * BK, n0);
-                        tma_load_2d(b_dst + B_HALF, &map_w, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + half_rows);
+                        load_w(b_dst, bar, kb * BK, n0);
+                        load_w(b_dst + B_HALF, bar, kb * BK, GATED ? up_row_offset + n0 : n0 + half_rows);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
