@@ -314,7 +314,7 @@ def main() -> int:
     if args.context is None:
         args.context = cfg.max_position_embeddings - (args.warmup + args.steps) - 2
     ps = args.page_size
-    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=64, cuda_graphs=not args.no_graphs)
+    engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=not args.no_graphs)
     pk = peaks()
     model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
     weight_bytes = model.weight_bytes()

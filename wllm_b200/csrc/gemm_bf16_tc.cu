@@ -351,6 +351,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int early = 0;
+            const bool once = tiles_m == 1;         // one tile of rows: every weight is read once, evicted first
+            const uint64_t stream = l2_evict_first();
+            auto load_w = [&](uint32_t dst, uint32_t bar, int x, int y) {
+                if (once) tma_load_2d_pair_hint(dst, &map_w, bar, x, y, stream);
+                else tma_load_2d_pair(dst, &map_w, bar, x, y);
+            };
             if (pair < num_tiles) {                 // W tiles of the first stages before the predecessor has finished
                 const int mn = pair % tiles_mn, split = pair / tiles_mn;
                 const int n0 = (mn / tiles_m) * tile_n;
@@ -358,7 +364,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 early = min(STAGES, kb_hi - kb_lo);
                 for (int i = 0; i < early; ++i) {
                     mbar_expect_tx_cluster(lead_full0 + 8 * i, STAGE_BYTES);
-                    tma_load_2d_pair(ring + i * STAGE_BYTES + A_BYTES, &map_w, lead_full0 + 8 * i, (kb_lo + i) * BK, n0 + w_row_offset);
+                    load_w(ring + i * STAGE_BYTES + A_BYTES, lead_full0 + 8 * i, (kb_lo + i) * BK, n0 + w_row_offset);
                 }
             }
             pdl_wait();
@@ -375,7 +381,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         if (!mbar_wait(empty0 + 8 * stage, phase ^ 1)) { ok = false; break; }
                         mbar_expect_tx_cluster(bar, STAGE_BYTES);
                         tma_load_2d_pair(a_dst, &map_a, bar, kb * BK, m0);
-                        tma_load_2d_pair(b_dst, &map_w, bar, kb * BK, n0 + w_row_offset);
+                        load_w(b_dst, bar, kb * BK, n0 + w_row_offset);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
