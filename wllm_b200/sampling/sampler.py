@@ -1,9 +1,11 @@
-"""Runs the sampling kernel over the logits rows of a step.
+"""Runs the sampling kernels over the logits rows of a step.
 
-One launch for all rows: per-row options, seeds, counters and the distinct generated
-ids (for the repetition penalty) travel in one int32 buffer; tokens and
-log-probabilities come back in one small copy.  The logits rows are modified in place
-where a repetition penalty applies.
+All rows go through the same two to five passes (statistics; up to three selection passes
+when some row asks for top-k, top-p or min-p; the draw), each one launch over all rows.
+Per-row options, seeds, counters and the distinct generated ids (for the repetition
+penalty) travel in one int32 buffer; tokens and log-probabilities come back in one small
+copy.  A batch of greedy rows without a penalty sends nothing and runs the first pass
+alone.  The logits rows are modified in place where a repetition penalty applies.
 """
 from __future__ import annotations
 
