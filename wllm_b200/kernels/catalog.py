@@ -14,6 +14,7 @@ FAMILIES = {
     "activation": [{}],
     "gemm_f32": [{}],
     "sampling": [{}],
+    "staging": [{}],
     "gemm_bf16_tc": [{}],
     # tensor-core attention is built per head size; others are built when a model first asks
     "attention_mma": [{"HEAD_DIM": 256}, {"HEAD_DIM": 32}, {"HEAD_DIM": 48}],

@@ -9,14 +9,14 @@ alone.  The logits rows are modified in place where a repetition penalty applies
 """
 from __future__ import annotations
 
-from ctypes import byref, c_int, c_void_p
+from ctypes import byref, c_int, c_longlong, c_void_p
 
 import numpy as np
 import torch
 
 from ..kernels import ops
 from ..kernels.build import load_family
-from ..engine.staging import PinnedRing
+from ..engine.staging import PinnedRing, new_event
 from .params import SamplingParams
 
 
@@ -24,14 +24,14 @@ class PendingSample:
     """The sampling of one step, enqueued: its tokens lie on the device (`tokens_device`, valid until the
     sampler's next launch) and are on their way to pinned host memory; `get()` waits for them."""
 
-    def __init__(self, rows: int, tokens_device, host: torch.Tensor | None, event):
-        self.rows, self.tokens_device, self._host, self._event = rows, tokens_device, host, event
+    def __init__(self, rows: int, tokens_device, host, done, lib):
+        self.rows, self.tokens_device, self._host, self._done, self._lib = rows, tokens_device, host, done, lib
 
     def get(self):
         if self.rows == 0:
             return [], []
-        self._event.synchronize()
-        out = self._host[:2 * self.rows].numpy()
+        ops._check(self._lib.wllm_event_wait(self._done), "waiting for the sampled ids")
+        out = self._host[:2 * self.rows]
         return out[:self.rows].tolist(), out[self.rows:].view(np.float32).tolist()
 
 
@@ -42,7 +42,7 @@ class Sampler:
         self._dev = self._out = None
         self._out_hosts = [None, None]   # two pinned result buffers: one is read while the next step fills the other
         self._turn = 0
-        self._side = None                # the results travel to the host on a stream of their own
+        self._side = self._side_raw = self._staging = None      # the results travel to the host on a stream of their own
         self._read = None                # behind the last copy out of `_out`: the next launch overwrites it
         self._scratch = None             # per-row state, chunk statistics and histograms; zero before first use
         self.h2d_bytes = 0
@@ -59,28 +59,30 @@ class Sampler:
         buffers alternate), and one's `tokens_device` is overwritten by the launch after it."""
         rows = logits.shape[0]
         if rows == 0:
-            return PendingSample(0, None, None, None)
-        main = torch.cuda.current_stream(self.device)
+            return PendingSample(0, None, None, None, None)
+        if self._side is None:
+            self._staging = load_family("staging")
+            self._side = torch.cuda.Stream(self.device)
+            self._side_raw = c_void_p(self._side.cuda_stream)
+            self._queued = new_event(self._staging)
+            self._done = [new_event(self._staging), new_event(self._staging)]
+        lib = self._staging
         if self._read is not None:
-            main.wait_event(self._read)          # the copy out of the previous results is done (it has long been)
+            # the copy out of the previous results is done (it has long been) before the next launch overwrites them
+            ops._check(lib.wllm_stream_wait(ops._stream(), self._read), "ordering the sampler behind its last copy")
         tokens = self.launch(logits, params, counters, seeds, generated)
         self._turn ^= 1
         host = self._out_hosts[self._turn]
-        if host is None or host.numel() < 2 * rows:
-            host = self._out_hosts[self._turn] = torch.empty(max(2 * rows, 1024), dtype=torch.int32).pin_memory()
-        if self._side is None:
-            self._side = torch.cuda.Stream(self.device)
-        sampled = torch.cuda.Event()
-        sampled.record(main)
-        # the copy to the host leaves the step's stream free for the next step's first kernels
-        self._side.wait_event(sampled)
-        with torch.cuda.stream(self._side):
-            host[:2 * rows].copy_(self._out[:2 * rows], non_blocking=True)
-            event = torch.cuda.Event()
-            event.record(self._side)
-        self._read = event
+        if host is None or host[0].numel() < 2 * rows:
+            pinned = torch.empty(max(2 * rows, 1024), dtype=torch.int32).pin_memory()
+            host = self._out_hosts[self._turn] = (pinned, pinned.numpy())
+        done = self._done[self._turn]
+        # the copy to the host runs on a stream of its own and leaves the step's stream free for the next step's first kernels
+        ops._check(lib.wllm_stage_fetch(c_void_p(host[0].data_ptr()), c_void_p(self._out.data_ptr()), c_longlong(8 * rows),
+                                        ops._stream(), self._side_raw, self._queued, done), "copy of the sampled ids")
+        self._read = done
         self.d2h_bytes = 8 * rows
-        return PendingSample(rows, tokens, host, event)
+        return PendingSample(rows, tokens, host[1], done, lib)
 
     def _scratch_for(self, rows: int, lib) -> c_void_p:
         need = int(lib.wllm_sample_scratch_row_bytes()) * max(rows, 64)
