@@ -129,6 +129,15 @@ def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: 
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
+
+    def table_width(tokens):       # captured decode steps are keyed by the block table's width, a power of two
+        width = 8
+        while width * page_size < tokens:
+            width *= 2
+        return width
+    if engine_cfg.cuda_graphs and table_width(context + warmup + 1) != table_width(context + warmup + steps):
+        print(f"note: the timed steps cross from {table_width(context + warmup + 1)} to {table_width(context + warmup + steps)} "
+              "pages a request: one of them captures a new graph, and the time per step includes that capture", file=sys.stderr)
     launches0, graph0 = ops.launches, runner.graph_launches
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler() as clocks:
