@@ -73,3 +73,25 @@ def test_prefill_share_plan_only_for_grids_that_fit_the_sms_once():
     assert ops.prefill_share_plan([2048] * 4, [2048] * 4, 8, 1, 64, False) == 0   # more CTAs than SMs anyway
     assert ops.prefill_share_plan([1, 1], [500, 600], 8, 1, 64, True) == 0     # single tokens are the decode kernel's
     assert ops.prefill_share_plan([2048], [2048], 8, 1, 48, False) == 0        # head sizes without the tcgen05 kernel
+
+
+def test_sampling_options_are_packed_row_by_row():
+    """The one int32 array that carries a step's sampling options to the device, and the bits that say which
+    selection passes some row needs."""
+    import numpy as np
+    from wllm_b200.sampling import SamplingParams
+    from wllm_b200.sampling.sampler import pack_options
+    params = [SamplingParams(temperature=0.5, top_k=7), SamplingParams(), SamplingParams(temperature=1.5, min_p=0.25, repetition_penalty=1.5)]
+    host, filters = pack_options(params, [4, 5, 6], [2 ** 40 + 3, 9, 2 ** 63 + 1], [{8, 2}, {1}, {30, 10, 20}])
+    rows, f = 3, host.view(np.float32)
+    assert f[0:3].tolist() == [0.5, 0.0, 1.5] and host[3:6].tolist() == [7, 0, 0]
+    assert f[6:9].tolist() == [1.0, 1.0, 1.0] and f[9:12].tolist() == [0.0, 0.0, 0.25] and f[12:15].tolist() == [1.0, 1.0, 1.5]
+    lo, hi = host[15:18].view(np.uint32).astype(np.uint64), host[18:21].view(np.uint32).astype(np.uint64)
+    assert ((hi << np.uint64(32)) | lo).tolist() == [2 ** 40 + 3, 9, 2 ** 63 + 1]
+    assert host[21:24].tolist() == [4, 5, 6]
+    # generated ids travel only for rows with a penalty, sorted, behind their offsets
+    assert host[8 * rows:9 * rows + 1].tolist() == [0, 0, 0, 3] and host[9 * rows + 1:].tolist() == [10, 20, 30]
+    assert filters == 3                                   # a row with top-k: all three selection passes
+    assert pack_options(params[1:], [0, 0], [0, 0], [set(), set()])[1] == 1        # min-p alone: the first pass only
+    assert pack_options([SamplingParams(temperature=0.7)], [0], [0], [set()])[1] == 0
+    assert pack_options([SamplingParams(temperature=0.0, top_k=5)], [0], [0], [set()])[1] == 0   # greedy rows ask for none
