@@ -1,14 +1,13 @@
 """Shared by the tests: tiny model folders, plain-implementation logits, host-side runners."""
 from __future__ import annotations
 
-import functools
 import os
 
 import torch
 from safetensors.torch import load_file
 
 import plain_gemma as plain
-from tiny_configs import CONFIGS, PAGE_SIZES, SEEDS
+from tiny_configs import CONFIGS, SEEDS
 
 
 def make_folder(tmp_path, name: str, dtype=torch.bfloat16) -> str:

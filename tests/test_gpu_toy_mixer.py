@@ -7,7 +7,6 @@ here, written to a model folder by the random-weights mode, loaded, and stepped 
 every way of cutting; the logits are compared with a plain whole-sequence statement of
 the same toy model, and in 32-bit with each other bit for bit.  The toy is no model of
 anyone's; it exists to exercise the seams."""
-import math
 from dataclasses import asdict, dataclass
 
 import pytest

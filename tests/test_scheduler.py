@@ -4,7 +4,7 @@ and what happens when pages run out."""
 import pytest
 import torch
 
-from wllm_b200.cache import CacheGroupSpec, CacheManager, OutOfPages
+from wllm_b200.cache import CacheGroupSpec, CacheManager
 from wllm_b200.engine.request import Request, RequestStatus
 from wllm_b200.engine.scheduler import Scheduler
 from wllm_b200.sampling import SamplingParams

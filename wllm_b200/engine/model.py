@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..cache import CacheGroupSpec, StateSpec
-from ..parts import BLOCKS, NORMS, CacheRef, KVNeed, ModelPlan, ParamSpec, Residual, StateNeed
+from ..parts import BLOCKS, NORMS, CacheRef, KVNeed, ModelPlan, Residual, StateNeed
 from ..parts.embedding import LogitsHead, ScaledEmbedding
 
 

@@ -41,7 +41,6 @@ from __future__ import annotations
 import random
 
 from ..cache import OutOfPages
-from ..sampling.params import SamplingParams
 from .request import Request, RequestStatus
 from .runner import StepEntry
 

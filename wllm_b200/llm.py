@@ -13,8 +13,6 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-import torch
-
 from .config import EngineConfig
 from .engine.build import build_model, build_runner
 from .engine.request import Request

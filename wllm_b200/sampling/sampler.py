@@ -17,7 +17,6 @@ import torch
 from ..kernels import ops
 from ..kernels.build import load_family
 from ..engine.staging import PinnedRing, new_event
-from .params import SamplingParams
 
 
 class PendingSample:
