@@ -33,6 +33,16 @@ def new_event(lib) -> c_void_p:
     return ev
 
 
+def free_events(lib, events) -> None:
+    """Hand events back (at the end of their owner's life; an event still in use is freed when its work is done)."""
+    for ev in events:
+        if lib is not None and ev is not None:
+            try:
+                lib.wllm_event_destroy(ev)
+            except Exception:       # the interpreter or the CUDA context is already going away
+                pass
+
+
 class PinnedRing:
     def __init__(self, device, slots: int = 4):
         self.device = torch.device(device)
@@ -46,6 +56,9 @@ class PinnedRing:
         self._side = self._side_raw = None
         self._lib = None
         self._next = 0
+
+    def __del__(self):
+        free_events(self._lib, self._arrived + self._consumed)
 
     def send(self, host: np.ndarray, dst: torch.Tensor) -> None:
         """Copy the int32 array `host` into the front of the device tensor `dst`."""

@@ -16,15 +16,16 @@ import torch
 
 from ..kernels import ops
 from ..kernels.build import load_family
-from ..engine.staging import PinnedRing, new_event
+from ..engine.staging import PinnedRing, free_events, new_event
 
 
 class PendingSample:
     """The sampling of one step, enqueued: its tokens lie on the device (`tokens_device`, valid until the
     sampler's next launch) and are on their way to pinned host memory; `get()` waits for them."""
 
-    def __init__(self, rows: int, tokens_device, host, done, lib):
+    def __init__(self, rows: int, tokens_device, host, done, lib, owner=None):
         self.rows, self.tokens_device, self._host, self._done, self._lib = rows, tokens_device, host, done, lib
+        self._owner = owner          # the sampler (and with it the event) lives as long as its results are awaited
 
     def get(self):
         if self.rows == 0:
@@ -46,6 +47,10 @@ class Sampler:
         self._scratch = None             # per-row state, chunk statistics and histograms; zero before first use
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+
+    def __del__(self):
+        if self._staging is not None:
+            free_events(self._staging, [self._queued] + self._done)
 
     def sample(self, logits: torch.Tensor, params: list, counters: list, seeds: list, generated: list):
         """logits [rows, vocab] float32 on the device; params[i]: SamplingParams; counters[i]: index of
@@ -81,7 +86,7 @@ class Sampler:
                                         ops._stream(), self._side_raw, self._queued, done), "copy of the sampled ids")
         self._read = done
         self.d2h_bytes = 8 * rows
-        return PendingSample(rows, tokens, host[1], done, lib)
+        return PendingSample(rows, tokens, host[1], done, lib, self)
 
     def _scratch_for(self, rows: int, lib) -> c_void_p:
         need = int(lib.wllm_sample_scratch_row_bytes()) * max(rows, 64)
