@@ -134,11 +134,9 @@ class ModelRunner:
         return buf[:n].view(shape)
 
     # -- batch building --------------------------------------------------------------
-    def _build(self, entries: list, table_width: int | None = None, device_tokens=None,
-               pad_requests: int | None = None) -> StepContext:
-        """`pad_requests` (a decode step under a captured graph): the arrays are laid out for that many requests;
-        the ones behind the real entries bring no token (q_len 0, no cache slot), so every kernel passes them
-        by, and the logits of all rows are wanted (the caller keeps the real ones)."""
+    def _host_arrays(self, entries: list, table_width: int | None, pad_requests: int | None):
+        """The step's index arrays in one int32 host array: (array, {name: (offset, length)}, names in order,
+        (tokens, requests, table width), patches)."""
         cache, ps = self.cache, self.cache.page_size
         G, real = len(cache.groups), len(entries)
         lens = [len(e.tokens) for e in entries]
@@ -212,15 +210,40 @@ class ModelRunner:
             view("patch_dst")[:len(patches)] = [starts[r] for r, _ in patches]
             view("patch_src")[:len(patches)] = [row for _, row in patches]
 
+        return host, offsets, [k for k, _ in sizes], (N, R, P), patches
+
+    def _send(self, host, offsets, patches, device_tokens) -> None:
+        """The host array to the device's index buffer; tokens that lie on the device are put in their places."""
+        total = host.shape[0]
         if self._meta is None or self._meta.numel() < total:
             cap = max(total, 4096, 2 * (self._meta.numel() if self._meta is not None else 0))
             self._graphs.clear()      # captured steps point into the old index buffer
             self._meta = torch.empty(cap, dtype=torch.int32, device=self.device)
         self._ring.send(host, self._meta)
         self.h2d_bytes = total * 4
+        if patches:
+            def dev(name, n):
+                o = offsets[name][0]
+                return self._meta[o:o + n]
+            ops.patch_tokens(dev("token_ids", offsets["token_ids"][1]), dev("patch_dst", len(patches)), device_tokens,
+                             dev("patch_src", len(patches)))
 
+    def _build(self, entries: list, table_width: int | None = None, device_tokens=None,
+               pad_requests: int | None = None) -> StepContext:
+        """`pad_requests` (a decode step under a captured graph): the arrays are laid out for that many requests;
+        the ones behind the real entries bring no token (q_len 0, no cache slot), so every kernel passes them
+        by, and the logits of all rows are wanted (the caller keeps the real ones)."""
+        host, offsets, names, (N, R, P), patches = self._host_arrays(entries, table_width, pad_requests)
+        self._send(host, offsets, patches, device_tokens)
+        ps, real = self.cache.page_size, len(entries)
+        lens = [len(e.tokens) for e in entries]
+        G = len(self.cache.groups)
+
+        def view(name):
+            o, n = offsets[name]
+            return host[o:o + n]
         ctx = StepContext(self)
-        ctx.n_tokens, ctx.n_requests, ctx.host = N, R, {k: view(k) for k, _ in sizes}
+        ctx.n_tokens, ctx.n_requests, ctx.host = N, R, {k: view(k) for k in names}
         ctx.host["max_pages"] = P
         ctx.num_single = sum(1 for n in lens if n == 1)
         ctx.num_multi = real - ctx.num_single
@@ -236,9 +259,6 @@ class ModelRunner:
         ctx.req_ctx_len, ctx.req_slot, ctx.want_rows = dev("req_ctx_len"), dev("req_slot"), dev("want_rows")
         ctx.group_slots = [dev(f"slots{g}") for g in range(G)]
         ctx.group_tables = [dev(f"table{g}").view(R, P) for g in range(G)]
-        if patches:
-            ops.patch_tokens(ctx.token_ids, dev("patch_dst")[:len(patches)], device_tokens,
-                             dev("patch_src")[:len(patches)])
         return ctx
 
     def _table_copy(self, rc, group: int) -> np.ndarray:
@@ -298,9 +318,14 @@ class ModelRunner:
         while bucket < len(entries):
             bucket = bucket * 3 // 2 if bucket & (bucket - 1) == 0 and bucket > 1 else (bucket * 4 // 3 if bucket > 2 else bucket + 1)
         key = (bucket, width)
-        ctx = self._build(entries, table_width=width, device_tokens=device_tokens, pad_requests=bucket)
         rec = self._graphs.get(key)
+        if rec is not None:
+            # a replay reads the index buffer at the addresses of its capture: the arrays go there, nothing else is built
+            host, offsets, _, _, patches = self._host_arrays(entries, width, bucket)
+            self._send(host, offsets, patches, device_tokens)
+            rec = self._graphs.get(key)         # the send may have had to grow the buffer, which drops the captures
         if rec is None:
+            ctx = self._build(entries, table_width=width, device_tokens=device_tokens, pad_requests=bucket)
             arena, saved = {}, self._arena
             self._arena = arena
             try:
