@@ -83,7 +83,7 @@ def paged_attention(q, out, k_pages, v_pages, token_req, positions, block_table,
 
 
 def paged_attention_simt(q, out, k_pages, v_pages, token_req, positions, block_table, nq, nkv, hd, page_size, window,
-                         scale):
+                         scale, scratch=None, max_chunks=0):
     return paged_attention(q, out, k_pages, v_pages, token_req, positions, block_table, nq, nkv, hd, page_size, window,
                            scale)
 

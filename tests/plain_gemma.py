@@ -32,7 +32,7 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 def rope_tables(positions: torch.Tensor, head_dim: int, theta: float):
     """inv_freq[j] = theta^(-2j/head_dim); angle = pos * inv_freq, duplicated
     over both halves (src/wllm/models/llama.py:55, 58-62)."""
-    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=positions.device) / head_dim))
     ang = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     ang = torch.cat((ang, ang), dim=-1)
     return ang.cos(), ang.sin()
@@ -59,7 +59,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int | N
     nkv = k.shape[1]
     rep = nq // nkv
     out = torch.empty_like(q)
-    idx = torch.arange(T)
+    idx = torch.arange(T, device=q.device)
     mask = idx[None, :] <= idx[:, None]
     if window is not None:
         mask &= idx[None, :] > idx[:, None] - window
@@ -118,9 +118,10 @@ def logits_head(h: torch.Tensor, w: dict, cfg: dict) -> torch.Tensor:
 def forward(ids: list[int] | torch.Tensor, w: dict, cfg: dict, dtype=torch.float32) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence (src/wllm/models/llama.py:405-415,
     432-434).  `cfg` is the raw config.json dictionary with head_dim filled in."""
-    ids = torch.as_tensor(ids, dtype=torch.long)
+    where = w["model.embed_tokens.weight"].device     # the host in the tests of the tiny models; any device works
+    ids = torch.as_tensor(ids, dtype=torch.long).to(where)
     w = {k: t.to(dtype) for k, t in w.items()}
-    positions = torch.arange(ids.shape[0])
+    positions = torch.arange(ids.shape[0], device=where)
     x = embed(ids, w["model.embed_tokens.weight"], cfg["hidden_size"])
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, i, positions, cfg)

@@ -219,6 +219,31 @@ def test_paged_attention_simt(dtype, case, window):
     torch.testing.assert_close(got.cpu().double(), want, **t)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 300])
+def test_paged_attention_simt_split_by_chunks_is_the_walk_bit_for_bit(dtype, window):
+    """A warp per (row, chunk of 256 keys) plus the merge kernel gives what one warp per row gives: contexts that
+    end inside the first chunk, on a chunk's edge and far behind it, a spike key in the first chunk."""
+    nq, nkv, hd, ps = 4, 2, 64, 16
+    ctx_lens, q_lens = [1000, 257, 256, 3, 513], [1, 2, 1, 3, 1]
+    q, kp, vp, treq, pos, table = _paged_case(dtype, nq, nkv, hd, ps, ctx_lens, q_lens, seed=9, spike=(window == 0))
+    scale = 1.0 / math.sqrt(hd)
+    args = (kp.to(DEV), vp.to(DEV), treq.to(DEV), pos.to(DEV), table.to(DEV), nq, nkv, hd, ps, window, scale)
+    walk = torch.empty(q.shape[0], nq * hd, dtype=dtype, device=DEV)
+    ops().paged_attention_simt(q.to(DEV), walk, *args)
+    want = ref.paged_attention(q, torch.empty(q.shape[0], nq * hd, dtype=torch.float64), kp, vp, treq, pos, table,
+                               nq, nkv, hd, ps, window, scale, dtype=torch.float64)
+    t = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+    torch.testing.assert_close(walk.cpu().double(), want, **t)
+    chunks = ops().simt_chunks(max(ctx_lens), window)
+    assert chunks == (4 if window == 0 else 3)
+    for bound in (chunks, chunks + 2):
+        scratch = torch.full((q.shape[0] * nq * bound * (hd + 2),), float("nan"), device=DEV)
+        split = torch.full_like(walk, float("nan"))
+        ops().paged_attention_simt(q.to(DEV), split, *args, scratch=scratch, max_chunks=bound)
+        assert torch.equal(split, walk)
+
+
 def test_paged_attention_refuses_unsupported_head_size():
     from wllm_b200.kernels import KernelError
     q = torch.zeros(1, 40, device=DEV)
@@ -239,7 +264,8 @@ def test_gated_act(dtype, act, n, I):
     torch.testing.assert_close(got.cpu().float(), want.float(), **tol(dtype))
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 512, 64), (33, 1000, 96), (130, 257, 144), (7, 129, 50), (300, 300, 1027)])
+@pytest.mark.parametrize("M,N,K", [(1, 512, 64), (33, 1000, 96), (130, 257, 144), (7, 129, 50), (300, 300, 1027),
+                                   (12, 3080, 520), (20, 100, 136), (32, 48, 2048), (64, 250, 1000), (5, 7, 4)])
 def test_gemm_f32_is_true_32bit_and_row_invariant(M, N, K):
     g = torch.Generator().manual_seed(5)
     a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)

@@ -67,8 +67,13 @@ class StepContext:
         others to the tiled prefill kernel; both find their requests by q_len on the device."""
         ps = self.cache.page_size
         if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
+            # few rows over long contexts (decoding): a warp per chunk of 256 keys instead of a warp per row
+            rows, chunks = q.shape[0] * nq, ops.simt_chunks(self.max_ctx, window)
+            scratch = None
+            if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
+                scratch = self.buffer("attention_chunks", (rows * chunks * (hd + 2),), torch.float32)
             ops.paged_attention_simt(q, out, k_pages, v_pages, self.token_req, self.positions,
-                                     self.group_tables[group], nq, nkv, hd, ps, window, scale)
+                                     self.group_tables[group], nq, nkv, hd, ps, window, scale, scratch, chunks)
             return
         table = self.group_tables[group]
         decode = self.num_single > 0 and nq // nkv <= 16

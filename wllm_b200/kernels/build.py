@@ -132,8 +132,8 @@ def compile_family(family: str, defines: dict | None = None, verbose: bool = Tru
                 raise KernelBuildError(f"nvcc failed on {source} (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")
             os.replace(tmp, out)
             prefix = name.rsplit("-", 1)[0] + "-"
-            for old in os.listdir(out_dir):      # objects of earlier versions of this family and variant
-                if old.startswith(prefix) and old.endswith(".so") and old != name:
+            for old in os.listdir(out_dir):      # objects of earlier versions of this family and variant, and their locks
+                if old.startswith(prefix) and old.endswith((".so", ".so.lock")) and not old.startswith(name):
                     try:
                         os.unlink(os.path.join(out_dir, old))
                     except OSError:

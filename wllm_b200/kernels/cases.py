@@ -6,6 +6,8 @@ print what it achieved against the roofline.  The same command under `ncu` gives
     python -m wllm_b200.kernels.cases attention-decode --requests 16 --context 8192
     python -m wllm_b200.kernels.cases attention-prefill --requests 1 --tokens 2048 --context 2048
     python -m wllm_b200.kernels.cases sampling --rows 8 --vocab 256000 --top-k 50 --top-p 0.9
+    python -m wllm_b200.kernels.cases gemm-f32 --m 16 --n 49152 --k 3072
+    python -m wllm_b200.kernels.cases attention-f32 --requests 16 --context 6000 --tokens 1 --heads 16 --kv-heads 16
 
 Operands are larger than L2 where the case is bound by memory (several weight copies are cycled), so the
 figures are DRAM figures.  Peaks: MEASURED_PEAKS.json at the repository root when present, else the fallback
@@ -77,6 +79,55 @@ def gemm(args) -> None:
     print(f"gemm_bf16_tc M={M} N={N} K={K} epilogue={code} parts={parts}: {ms * 1e3:.1f} us, "
           f"{flops / ms / 1e9:.1f} TFLOP/s ({flops / ms / 1e9 / tf:.3f} of {src} {tf:.0f}), "
           f"{byts / ms / 1e6:.0f} GB/s ({byts / ms / 1e6 / hbm:.3f} of {src} {hbm:.0f}), status {ops.tc_gemm_status(DEV)}")
+
+
+def gemm_f32(args) -> None:
+    """The 32-bit FMA product against a measured loop of fused multiply-adds (no tensor cores)."""
+    M, N, K = args.m, args.n, args.k
+    a = torch.randn(M, K, device=DEV) * 0.1
+    copies = max(1, min(8, int(300e6 // (N * K * 4)) + 1))
+    ws = [torch.randn(N, K, device=DEV) * 0.1 for _ in range(copies)]
+    out = torch.empty((M, N), device=DEV)
+    i = [0]
+
+    def run():
+        i[0] += 1
+        ops.gemm_f32(a, ws[i[0] % copies], out)
+    ms = timed(run, args.iters)
+    hbm, _, src = peaks()
+    fma_peak = ops.fma_peak_tflops(DEV)
+    flops, byts = 2.0 * M * N * K, (N * K + M * K + M * N) * 4.0
+    print(f"gemm_f32 M={M} N={N} K={K}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.2f} TFLOP/s "
+          f"({flops / ms / 1e9 / fma_peak:.3f} of a measured FMA loop's {fma_peak:.1f}), "
+          f"{byts / ms / 1e6:.0f} GB/s ({byts / ms / 1e6 / hbm:.3f} of {src} {hbm:.0f})")
+
+
+def attention_f32(args) -> None:
+    """The 32-bit attention (one warp per row, or per row and chunk of 256 keys) as a step context would call it."""
+    nq, nkv, hd, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
+    R, ctx, q_len = args.requests, args.context, args.tokens
+    pages_each = -(-ctx // ps)
+    num_pages = R * pages_each + 1
+    k = torch.randn(num_pages, nkv, ps, hd, device=DEV) * 0.5
+    v = torch.randn(num_pages, nkv, ps, hd, device=DEV) * 0.5
+    table = torch.randperm(num_pages - 1, device=DEV).to(torch.int32).view(R, pages_each).contiguous()
+    n = R * q_len
+    q = torch.randn(n, nq * hd, device=DEV) * 0.5
+    out = torch.empty_like(q)
+    treq = torch.arange(R, dtype=torch.int32, device=DEV).repeat_interleave(q_len)
+    pos = (torch.arange(ctx - q_len, ctx, dtype=torch.int32, device=DEV)).repeat(R)
+    rows, chunks = n * nq, ops.simt_chunks(ctx, 0)
+    scratch = None
+    if not args.walk and chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
+        scratch = torch.empty(rows * chunks * (hd + 2), device=DEV)
+    ms = timed(lambda: ops.paged_attention_simt(q, out, k, v, treq, pos, table, nq, nkv, hd, ps, 0, 1.0 / math.sqrt(hd),
+                                                scratch, chunks), args.iters)
+    hbm, _, src = peaks()
+    kv_bytes = 2.0 * R * ctx * nkv * hd * 4
+    keys_seen = R * sum(ctx - q_len + i + 1 for i in range(q_len))
+    print(f"attention f32 requests={R} context={ctx} tokens={q_len} heads={nq}/{nkv} head_dim={hd} "
+          f"{'split by chunks' if scratch is not None else 'walk'}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of keys "
+          f"and values ({kv_bytes / ms / 1e6 / hbm:.3f} of {src} {hbm:.0f}), {4.0 * nq * hd * keys_seen / ms / 1e9:.2f} TFLOP/s")
 
 
 def attention(args, decode: bool) -> None:
@@ -154,7 +205,11 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--epilogue", default="bf16", choices=["bf16", "f32", "gelu_tanh", "silu"])
     g.add_argument("--split", action="store_true", help="cut K into parts as a step of few rows does (float32 slabs)")
-    for name in ("attention-decode", "attention-prefill"):
+    g32 = sub.add_parser("gemm-f32")
+    g32.add_argument("--m", type=int, default=16)
+    g32.add_argument("--n", type=int, default=49152)
+    g32.add_argument("--k", type=int, default=3072)
+    for name in ("attention-decode", "attention-prefill", "attention-f32"):
         a = sub.add_parser(name)
         a.add_argument("--requests", type=int, default=16)
         a.add_argument("--context", type=int, default=8192)
@@ -164,6 +219,7 @@ def main(argv=None) -> int:
         a.add_argument("--head-dim", type=int, default=256)
         a.add_argument("--page-size", type=int, default=64)
         a.add_argument("--no-share", action="store_true", help="prefill: never share a heavy tile between two CTAs")
+        a.add_argument("--walk", action="store_true", help="attention-f32: one warp per row even where chunks would be split")
     sm = sub.add_parser("sampling")
     sm.add_argument("--rows", type=int, default=8)
     sm.add_argument("--vocab", type=int, default=256000)
@@ -179,6 +235,10 @@ def main(argv=None) -> int:
         return 1
     if args.case == "gemm":
         gemm(args)
+    elif args.case == "gemm-f32":
+        gemm_f32(args)
+    elif args.case == "attention-f32":
+        attention_f32(args)
     elif args.case == "sampling":
         sampling(args)
     else:

@@ -148,20 +148,41 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
            "rope_kv_write")
 
 
+SIMT_CHUNK = 256   # keys per chunk of the one-warp-per-row attention (csrc/attention_simt.cu)
+
+
+def simt_chunks(max_ctx: int, window: int) -> int:
+    """Upper bound of the chunks of 256 keys that a row of a step touches, from the longest context of the
+    step (and the window, if the layer has one)."""
+    most = -(-max(1, max_ctx) // SIMT_CHUNK)
+    return min(most, -(-window // SIMT_CHUNK) + 1) if window > 0 else most
+
+
 def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                          token_req: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
-                         nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float) -> torch.Tensor:
-    """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd]."""
-    _need_cuda(q, out, k_pages, v_pages, token_req, positions, block_table)
+                         nq: int, nkv: int, hd: int, page_size: int, window: int, scale: float,
+                         scratch: torch.Tensor | None = None, max_chunks: int = 0) -> torch.Tensor:
+    """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd].
+    With `scratch` (float32, n * nq * max_chunks * (hd + 2) floats) and max_chunks = simt_chunks(...) > 1 every
+    (row, chunk of 256 keys) gets a warp of its own and a second kernel merges them; the result is the same,
+    bit for bit, as without."""
+    _need_cuda(q, out, k_pages, v_pages, token_req, positions, block_table, scratch)
     n = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
+    if scratch is not None:
+        assert scratch.dtype == torch.float32 and scratch.is_contiguous() and max_chunks >= 1
+        assert scratch.numel() >= n * nq * max_chunks * (hd + 2)
     lib = load_family("attention_simt")
     _check(lib.wllm_paged_attention_simt(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
                                          _dt(q), _ptr(_int32(token_req, "token_req")),
                                          _ptr(_int32(positions, "positions")), _ptr(_int32(block_table, "block_table")),
                                          block_table.shape[1], n, nq, nkv, hd, page_size, window, c_float(scale),
+                                         _ptr(scratch), max_chunks if scratch is not None else 0,
                                          _stream()), f"paged_attention_simt(head_dim={hd}, heads={nq}/{nkv})")
+    if scratch is not None and max_chunks > 1:
+        global launches
+        launches += 1    # the merge kernel
     return out
 
 
@@ -310,9 +331,34 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) 
         out = torch.empty((M, N), dtype=torch.float32, device=a.device)
     assert out.stride(1) == 1 and out.shape == (M, N) and out.dtype == torch.float32
     lib = load_family("gemm_f32")
-    _check(lib.wllm_gemm_f32(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _stream()),
-           "gemm_f32")
+    lib.wllm_gemm_f32_scratch_floats.restype = ctypes.c_longlong
+    need = lib.wllm_gemm_f32_scratch_floats(M, N, K)       # partial sums of the few-rows kernel when K has several segments
+    scratch = torch.empty(need, dtype=torch.float32, device=a.device) if need else None
+    _check(lib.wllm_gemm_f32(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N, K, _ptr(scratch),
+                             ctypes.c_longlong(need), _stream()), "gemm_f32")
+    if need:
+        global launches
+        launches += 1        # the kernel that adds the partial sums
     return out
+
+
+def fma_peak_tflops(device, iters: int = 20000) -> float:
+    """TFLOP/s of a loop of independent 32-bit fused multiply-adds on every SM (csrc/gemm_f32.cu): what the
+    32-bit products are measured against, at the clock the device runs such a loop at."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    blocks = sms * 8
+    out = torch.empty(blocks * 256, dtype=torch.float32, device=device)
+    lib = load_family("gemm_f32")
+    best = 0.0
+    with torch.cuda.device(device):
+        for _ in range(4):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            _check(lib.wllm_fma_loop(_ptr(out), blocks, iters, _stream()), "fma_loop")
+            end.record()
+            torch.cuda.synchronize()
+            best = max(best, blocks * 256 * 8 * 2.0 * iters / (start.elapsed_time(end) * 1e-3) / 1e12)
+    return best
 
 
 _TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3}
