@@ -87,6 +87,35 @@ def test_scarce_pages_preempt_and_change_nothing(folders):
     assert tight_engine.runner.cache.free_pages() == [12]
 
 
+@pytest.mark.parametrize("dtype,margin", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_scarce_pages_with_poisoned_pages(folders, dtype, margin):
+    """The same shortage with pages that hold NaN until written and again once given back (a preempted
+    request's pages go to its neighbours at once): every token is still what the plain implementation draws."""
+    prompts = prompts_of("A", (30, 41, 22, 35), seed=4)
+    sp = SamplingParams(temperature=0.7, seed=9, max_tokens=40, ignore_eos=True)
+    engine = llm(folders["A"], dtype=dtype, block_size=16, num_blocks=12, admission="optimistic",
+                 chunked_prefill_tokens=24, poison_pages=True)
+    outs = engine.generate(prompts, sp)
+    assert engine.stats["preemptions"] >= 1 and engine.runner.cache.free_pages() == [12]
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 40
+        check_against_plain("A", folders["A"], p, o.token_ids, sp, sp.seed, margin)
+
+
+def test_a_kernel_that_gave_up_waiting_stops_generation(folders):
+    """The status word that bounded waits in the tensor-core kernels set travels back with every step's sampled
+    ids; a step that finds it set raises instead of handing on tokens made from partial results, and clears it."""
+    from wllm_b200.kernels import KernelError, ops
+    engine = llm(folders["A"], dtype="bfloat16")
+    ops._status_word(engine.engine_config.device).fill_(21)
+    with pytest.raises(KernelError, match="gave up waiting.*decode attention"):
+        engine.generate([[5, 6, 7]], SamplingParams(max_tokens=3, ignore_eos=True))
+    assert ops.tc_gemm_status(engine.engine_config.device) == 0
+    outs = llm(folders["A"], dtype="bfloat16", async_scheduling=True).generate([[5, 6, 7]],
+                                                                             SamplingParams(max_tokens=3, ignore_eos=True))
+    assert len(outs[0].token_ids) == 3
+
+
 def test_eos_and_stop_ids_end_a_request(folders):
     p = prompts_of("A", (9,))[0]
     sp = dict(temperature=1.5, seed=3, max_tokens=12)
@@ -143,6 +172,61 @@ def test_captured_decode_steps_change_nothing(folders, dtype):
     outs = graphed.generate(prompts, sp)
     assert graphed.runner.graph_launches > 0
     assert [o.token_ids for o in outs] == [o.token_ids for o in plain_run]
+
+
+@pytest.mark.parametrize("dtype,margin", [("float32", 1e-4), ("bfloat16", 3e-2)])
+def test_captured_steps_across_table_widths_batch_buckets_and_a_regrown_index_buffer(folders, dtype, margin):
+    """Eight requests that grow from one to three pages to more than sixteen (captures for tables of 8, 16 and
+    32 pages) and end one after the other (captures for 8, 6, 4, 3, 2 and 1 requests).  Then, on the same
+    engine, three long prompts whole in one step: their index arrays outgrow the buffer that the captures
+    point into, which drops every capture, and the decode steps behind them are captured anew.  In 32-bit
+    the tokens are the eager engine's; in both precisions they are what the plain implementation draws."""
+    lengths, news = (5, 40, 77, 3, 21, 9, 60, 33), (300, 33, 150, 12, 250, 80, 40, 200)
+    prompts = prompts_of("B", lengths, seed=6)
+    sps = [SamplingParams(temperature=0.8, seed=70 + i, max_tokens=n, ignore_eos=True) for i, n in enumerate(news)]
+    kw = dict(dtype=dtype, block_size=16, num_blocks=240, max_num_seqs=16)
+    eager, graphed = llm(folders["B"], **kw), llm(folders["B"], cuda_graphs=True, **kw)
+    want, outs = eager.generate(prompts, sps), graphed.generate(prompts, sps)
+    keys = set(graphed.runner._graphs)
+    assert {w for _, w in keys} >= {8, 16, 32}, keys
+    assert {b for b, _ in keys} >= {1, 2, 3, 4, 6, 8}, keys
+    meta = graphed.runner._meta.numel()
+    long_prompts = prompts_of("B", (480, 470, 460), seed=7)
+    sp2 = SamplingParams(temperature=0.8, seed=90, max_tokens=20, ignore_eos=True)
+    want += eager.generate(long_prompts, sp2)
+    outs += graphed.generate(long_prompts, sp2)
+    assert graphed.runner._meta.numel() > meta, "the long prompts were meant to outgrow the index buffer"
+    assert graphed.runner._graphs and all(rec["meta"] is graphed.runner._meta for rec in graphed.runner._graphs.values())
+    assert graphed.runner.graph_launches > 0 and eager.runner.graph_launches == 0
+    if dtype == "float32":
+        assert [o.token_ids for o in outs] == [o.token_ids for o in want]
+    for p, o, sp in zip(prompts + long_prompts, outs, sps + [sp2] * 3):
+        assert len(o.token_ids) == sp.max_tokens
+        check_against_plain("B", folders["B"], p, o.token_ids, sp, sp.seed, margin)
+
+
+def test_the_command_line_generates_what_the_python_entry_point_does(folders):
+    """`python -m wllm_b200 --model DIR ...` in a process of its own: its JSON lines carry the tokens of
+    LLM.generate with the same options (random prompts from the same seed, portions of 16, captured graphs)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "wllm_b200", "--model", folders["B"], "--dtype", "float32", "--block-size", "32",
+           "--num-blocks", "24", "--prompt-lens", "5,40,77", "--prompt-seed", "3", "--prompt-ids", "7,8,9",
+           "--cuda-graphs", "--chunked-prefill-tokens", "16", "--temperature", "0.7", "--top-k", "40", "--seed", "11",
+           "--max-tokens", "12", "--ignore-eos", "--log-level", "WARNING"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(x) for x in proc.stdout.splitlines() if x.startswith("{")]
+    g = torch.Generator().manual_seed(3)
+    prompts = [[7, 8, 9]] + [torch.randint(0, CONFIGS["B"]["vocab_size"], (n,), generator=g).tolist() for n in (5, 40, 77)]
+    sp = SamplingParams(temperature=0.7, top_k=40, seed=11, max_tokens=12, ignore_eos=True)
+    outs = llm(folders["B"], dtype="float32", block_size=32, num_blocks=24, chunked_prefill_tokens=16,
+               cuda_graphs=True).generate(prompts, sp)
+    assert [x["token_ids"] for x in lines] == [o.token_ids for o in outs]
+    assert [x["prompt_tokens"] for x in lines] == [3, 5, 40, 77] and all(x["finish_reason"] == "length" for x in lines)
 
 
 @pytest.mark.parametrize("graphs", [False, True])

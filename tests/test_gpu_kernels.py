@@ -222,7 +222,7 @@ def test_paged_attention_simt(dtype, case, window):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [0, 300])
 def test_paged_attention_simt_split_by_chunks_is_the_walk_bit_for_bit(dtype, window):
-    """A warp per (row, chunk of 256 keys) plus the merge kernel gives what one warp per row gives: contexts that
+    """A warp per (row, chunk of 64 keys) plus the merge kernel gives what one warp per row gives: contexts that
     end inside the first chunk, on a chunk's edge and far behind it, a spike key in the first chunk."""
     nq, nkv, hd, ps = 4, 2, 64, 16
     ctx_lens, q_lens = [1000, 257, 256, 3, 513], [1, 2, 1, 3, 1]
@@ -236,7 +236,7 @@ def test_paged_attention_simt_split_by_chunks_is_the_walk_bit_for_bit(dtype, win
     t = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
     torch.testing.assert_close(walk.cpu().double(), want, **t)
     chunks = ops().simt_chunks(max(ctx_lens), window)
-    assert chunks == (4 if window == 0 else 3)
+    assert chunks == (16 if window == 0 else 6)
     for bound in (chunks, chunks + 2):
         scratch = torch.full((q.shape[0] * nq * bound * (hd + 2),), float("nan"), device=DEV)
         split = torch.full_like(walk, float("nan"))
@@ -296,6 +296,8 @@ MMA_CASES = ATTN_CASES + [
     (16, 16, 256, 32, [200, 77], [5, 77]),
     (4, 2, 96, 16, [500, 333, 2], [1, 300, 2]),
     (4, 2, 128, 32, [700, 90], [300, 90]),          # head size 128, tiles of 256 rows on pairs of CTAs
+    (6, 2, 64, 16, [700, 65, 1, 300], [1, 1, 1, 1]),  # head size 64: the smallest that the TMA kernels take
+    (6, 2, 64, 32, [300, 130], [140, 2]),
 ]
 
 

@@ -212,6 +212,22 @@ def test_every_cut_of_the_toy_model_matches_its_plain_statement(toy, dtype, tol)
                 assert not bad, f"{name}: first differing (request, position) {bad[0]}"
 
 
+def test_a_model_with_state_of_its_own_is_never_replayed_from_a_captured_graph(toy):
+    """A captured decode step runs twice when it is captured and replays the launches its parts chose from host
+    data at that moment; a mixer that carries state from step to step would count a token twice and keep
+    writing to the slots of the capture.  So the runner steps such a model eagerly whatever was asked for, and
+    the tail decoded token by token still matches the plain statement."""
+    from test_gpu_replay import gpu_runner
+    folder, reqs, ref = toy
+    steps = traces.tail_singly(reqs, 16)
+    runner = gpu_runner(folder, torch.float32, 16, -(-traces.peak_tokens(steps) // 16))
+    assert not runner.model.graph_safe
+    runner.enable_graphs()
+    rows = traces.run_in_process(runner, steps)
+    assert runner.graph_launches == 0 and not runner._graphs
+    assert max_diff(rows, ref) < 5e-5
+
+
 def test_the_window_group_holds_fewer_pages_than_the_full_one(toy):
     from test_gpu_replay import gpu_runner
     folder, reqs, _ = toy

@@ -5,8 +5,11 @@ entry point, which takes its scratch from the caller.
 Some hosts may not allocate device memory at all (their memory is owned elsewhere, or they
 run where cudaMalloc is off limits); for them the partial results of the key splits live in
 a fixed array inside the library.  The two entry points run the same kernels, so their
-outputs must agree to the last bit; the comparison still uses the tolerance of the other
-kernel tests.  Two calls in a row share the array: the second must not see the first."""
+outputs must agree to the last bit; both are also held against the float64 statement of
+paged attention in tests/kernel_refs.py, within the tolerance of the other kernel tests (a
+fault in what the two share would otherwise pass).  Two calls in a row share the array:
+the second must not see the first.  A window, and a context beyond the caller's plan of
+splits, go through the fixed array as well."""
 import ctypes
 import math
 from ctypes import c_float, c_void_p
@@ -36,13 +39,13 @@ def _case(seed, nq, nkv, ps, ctx_lens):
     return q.to(DEV), k.to(DEV), v.to(DEV), table.to(DEV), meta
 
 
-def _call_static(lib, q, out, k, v, table, meta, nq, nkv, ps, scale, split_keys, max_splits):
+def _call_static(lib, q, out, k, v, table, meta, nq, nkv, ps, scale, split_keys, max_splits, window=0):
     starts, qlens, ctxs = meta
     p = lambda t: c_void_p(t.data_ptr())   # noqa: E731
     status = torch.zeros(1, dtype=torch.int32, device=DEV)     # stays 0 unless a bounded wait in the kernel ran out
     rc = lib.wllm_attention_mma_decode_static(
         p(q), q.stride(0), p(out), out.stride(0), p(k), p(v), ctypes.c_longlong(k.shape[0]), p(starts), p(qlens), p(ctxs),
-        p(table), table.shape[1], qlens.shape[0], nq, nkv, ps, 0, c_float(scale), split_keys, max_splits, p(status),
+        p(table), table.shape[1], qlens.shape[0], nq, nkv, ps, window, c_float(scale), split_keys, max_splits, p(status),
         c_void_p(torch.cuda.current_stream().cuda_stream))
     assert int(status.item()) == 0
     return rc
@@ -54,21 +57,28 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
     lib = load_family("attention_decode_static", {"HEAD_DIM": HD})
     assert isinstance(lib, ctypes.CDLL)
     lib.wllm_attention_mma_decode_static_needs.restype = ctypes.c_longlong
+    import kernel_refs as ref
     nq, nkv, ps, scale = 6, 2, 16, 1.0 / math.sqrt(HD)
-    for seed, ctx_lens, split_keys in ((1, [700, 65, 1, 300], 128), (2, [33, 512, 129], 64)):
+    # (seed, contexts, keys per split, splits, window); the last plan covers 256 keys of a 700-key context
+    for seed, ctx_lens, split_keys, max_splits, window in ((1, [700, 65, 1, 300], 128, 6, 0), (2, [33, 512, 129], 64, 8, 0),
+                                                          (3, [700, 40, 200], 64, 11, 50), (4, [700, 65], 64, 4, 0)):
         q, k, v, table, meta = _case(seed, nq, nkv, ps, ctx_lens)
-        max_splits = -(-max(ctx_lens) // split_keys)
         R = len(ctx_lens)
         want = torch.full((R, nq * HD), float("nan"), dtype=torch.bfloat16, device=DEV)
         scratch = torch.empty(ops.attention_mma_scratch_floats(R, nq, HD, max_splits), device=DEV)
-        ops.attention_mma_decode(q, want, k, v, *meta, table, nq, nkv, HD, ps, 0, scale, split_keys, max_splits, scratch)
+        ops.attention_mma_decode(q, want, k, v, *meta, table, nq, nkv, HD, ps, window, scale, split_keys, max_splits, scratch)
         assert lib.wllm_attention_mma_decode_static_needs(R, nq, max_splits) == scratch.numel()
         got = torch.full_like(want, float("nan"))
-        assert _call_static(lib, q, got, k, v, table, meta, nq, nkv, ps, scale, split_keys, max_splits) == 0
+        assert _call_static(lib, q, got, k, v, table, meta, nq, nkv, ps, scale, split_keys, max_splits, window) == 0
         torch.cuda.synchronize()
         assert not torch.isnan(got.float()).any()
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want)
+        positions = torch.tensor([c - 1 for c in ctx_lens], dtype=torch.int32)
+        exact = ref.paged_attention(q.cpu(), torch.empty(R, nq * HD, dtype=torch.float64), k.cpu(), v.cpu(),
+                                    torch.arange(R, dtype=torch.int32), positions, table.cpu(), nq, nkv, HD, ps, window,
+                                    scale, dtype=torch.float64)
+        torch.testing.assert_close(got.cpu().double(), exact, rtol=2e-2, atol=2e-2)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():

@@ -60,14 +60,25 @@ class RequestCache:
 
 
 class CacheGroup:
-    def __init__(self, spec: CacheGroupSpec, num_pages: int, page_size: int, dtype, device):
+    def __init__(self, spec: CacheGroupSpec, num_pages: int, page_size: int, dtype, device, poison: bool = False):
         self.spec = spec
         self.pool = PagePool(num_pages)
         self.page_size = page_size
         self.pages = None
+        self.poison = poison
         if device is not None:
-            self.pages = torch.zeros((spec.layers, 2, num_pages, spec.kv_heads, page_size, spec.head_dim),
-                                     dtype=dtype, device=device)
+            shape = (spec.layers, 2, num_pages, spec.kv_heads, page_size, spec.head_dim)
+            self.pages = torch.full(shape, float("nan"), dtype=dtype, device=device) if poison else \
+                torch.zeros(shape, dtype=dtype, device=device)
+
+    def give(self, pages: list) -> None:
+        """Pages go back to the pool; with `poison` their contents become NaN first (in stream order, so a step
+        still running has read them before)."""
+        if self.poison and self.pages is not None and pages:
+            index = torch.tensor(pages, dtype=torch.long, device=self.pages.device)
+            self.pages.index_fill_(2, index, float("nan"))
+        for page in pages:
+            self.pool.give(page)
 
     def keys(self, layer: int) -> torch.Tensor:
         return self.pages[layer, 0]
@@ -114,11 +125,14 @@ class StateSlots:
 
 class CacheManager:
     def __init__(self, groups: list, page_size: int, num_pages: int, max_requests: int, states: list = (),
-                 dtype=torch.bfloat16, device=None):
+                 dtype=torch.bfloat16, device=None, poison: bool = False):
+        """`poison` (a debugging aid; the tests switch it on): pools start as NaN instead of zeros and every
+        page is filled with NaN again when it is given back, so a kernel that reads a slot that was never
+        written, or a page that its request no longer holds, shows at once in the logits."""
         if page_size < 1:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
-        self.groups = [CacheGroup(g, num_pages, page_size, dtype, device) for g in groups]
+        self.groups = [CacheGroup(g, num_pages, page_size, dtype, device, poison) for g in groups]
         self.slots = StateSlots(max_requests, list(states), device)
         self.live: dict = {}
         self.dtype, self.device = dtype, device
@@ -138,9 +152,7 @@ class CacheManager:
         if rc.closed:
             raise RuntimeError(f"request {rc.request_id!r} closed twice")
         for g, table in zip(self.groups, rc.tables):
-            for page in reversed(table):
-                if page >= 0:
-                    g.pool.give(page)
+            g.give([page for page in reversed(table) if page >= 0])
             table.clear()
         self.slots.give(rc.slot)
         rc.closed = True
@@ -200,8 +212,9 @@ class CacheManager:
                 continue
             first_needed = rc.num_tokens - w + 1          # oldest key the next token reads
             upto = min(max(0, first_needed // self.page_size), len(rc.tables[gi]))
-            for i in range(rc.released_upto[gi], upto):
-                g.pool.give(rc.tables[gi][i])
+            passed = list(range(rc.released_upto[gi], upto))
+            g.give([rc.tables[gi][i] for i in passed])
+            for i in passed:
                 rc.tables[gi][i] = -1
                 rc.version += 1
             rc.released_upto[gi] = max(rc.released_upto[gi], upto)
@@ -211,9 +224,13 @@ class CacheManager:
         rc.reserved = 0
         target = -(-rc.num_tokens // self.page_size)
         for g, table in zip(self.groups, rc.tables):
+            surplus = []
             while len(table) > target:
-                g.pool.give(table.pop())
+                page = table.pop()
                 rc.version += 1
+                if page >= 0:          # (a window never passes a page that holds no committed token; checked all the same)
+                    surplus.append(page)
+            g.give(surplus)
 
     # -- figures -------------------------------------------------------------------
     def free_pages(self) -> list:

@@ -35,6 +35,7 @@ class EngineConfig:
     max_model_len: int | None = None     # None: the model's max_position_embeddings
     cuda_graphs: bool = False            # replay captured graphs for decode-only steps
     device: str = "cuda:0"
+    poison_pages: bool = False           # debugging: cache pages hold NaN until written and again once given back
 
     def __post_init__(self):
         self.dtype = parse_dtype(self.dtype)

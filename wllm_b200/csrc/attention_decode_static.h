@@ -24,6 +24,9 @@
  *     it has to start at zero: every split writes its slot before the merge reads it.
  *     Two calls that overlap on the GPU (different streams, no ordering between them)
  *     race on the array; order them.
+ *   - split_keys and max_splits are the caller's plan: every request is cut into parts of split_keys keys,
+ *     at most max_splits of them.  A request whose context is longer than split_keys * max_splits is still
+ *     computed in full (its parts are widened to fit max_splits), only more slowly than planned.
  *   - Returns 0 once the kernels are enqueued on `stream`, or a status code as the
  *     other entry points do (1000 + cudaError_t for a failed launch).
  */

@@ -328,13 +328,14 @@ constexpr int DEC_SMEM = 1024 + 16 * ROWB + DEC_STAGES * 2 * TILE_BYTES + 64;
 // tiles, so that a request shorter than the bound does not fill its first split and starve the rest; but not
 // in parts below 512 keys (or the planned size, if that is smaller): a CTA's fixed cost is worth about that
 // many.  A grid of more CTAs than SMs keeps the planned size: the host chose it so that the short rests,
-// which start last, fill the second round.
+// which start last, fill the second round; a context longer than planned size x splits (a caller's mistake:
+// it cannot see the lengths on the device) widens the parts instead of dropping keys.
 // (`split_keys` arrives negated when the grid is resident at once: the host knows, and the merge kernel, whose
 // grid differs, has to cut the same way.)
 __device__ __forceinline__ int keys_per_split(int ctx, int split_keys, int max_splits, int tile) {
-    if (split_keys > 0) return split_keys;
-    split_keys = -split_keys;
     const int even = ((ctx + max_splits - 1) / max_splits + tile - 1) / tile * tile;
+    if (split_keys > 0) return max(split_keys, even);   // never more splits than the launch has CTAs and slots for
+    split_keys = -split_keys;
     return max(min(split_keys, 512), even);
 }
 

@@ -8,7 +8,7 @@
 //
 // Scores, softmax statistics and the output accumulate in 32-bit (expf, no fast
 // math), in an order that is a function of the keys' absolute positions alone:
-//   chunk    256 keys that start at an absolute multiple of 256.  Its partial result
+//   chunk    64 keys that start at an absolute multiple of 64.  Its partial result
 //            (max m, sum l, output o) starts from nothing and takes the chunk's keys
 //            in tiles of 32 (absolute multiples of 32) with the running-maximum rule.
 //   row      the chunks' partial results merged one after the other in ascending
@@ -48,7 +48,7 @@ template <> struct Vec<bf16> {
 };
 
 constexpr int WARPS = 4;
-constexpr int CHUNK = 256;
+constexpr int CHUNK = 64;
 
 // The partial result of one chunk of one row (every lane holds m and l; lane x holds o of the dimensions e*32+x).
 template <typename T, int NE>
@@ -72,6 +72,7 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
             const T* kr = k_pages + (size_t)row * hd;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             float kv[Vec<T>::N];
+#pragma unroll 8
             for (int d = 0; d < hd; d += Vec<T>::N) {
                 Vec<T>::load(kr + d, kv);
 #pragma unroll
@@ -85,17 +86,28 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
         l = l * corr + warp_sum(p);
 #pragma unroll
         for (int e = 0; e < NE; ++e) o[e] *= corr;
+        // values of four keys are requested before the first of them is used; a key outside the row's range
+        // (only at its two ends) adds fma(0, v, o) = o with the values of a key inside it
         const int count = min(32, pos - tile + 1);
-        for (int j = 0; j < count; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
-            const int rj = __shfl_sync(0xffffffffu, row, j);
-            if (rj < 0) continue;
-            const T* vr = v_pages + (size_t)rj * hd;
+        const int safe = __shfl_sync(0xffffffffu, row, min(31, pos - tile));     // the row's last key of this tile: always valid
+        for (int j0 = 0; j0 < count; j0 += 4) {
+            float pj[4], vj[4][NE];
 #pragma unroll
-            for (int e = 0; e < NE; ++e) {
-                const int d = e * 32 + lane;
-                if (d < hd) o[e] = fmaf(pj, to_f32(vr[d]), o[e]);
+            for (int u = 0; u < 4; ++u) {
+                const int j = min(j0 + u, 31);
+                pj[u] = j0 + u < count ? __shfl_sync(0xffffffffu, p, j) : 0.f;
+                const int rj = __shfl_sync(0xffffffffu, row, j);
+                const T* vr = v_pages + (size_t)(rj < 0 || j0 + u >= count ? safe : rj) * hd;
+#pragma unroll
+                for (int e = 0; e < NE; ++e) {
+                    const int d = e * 32 + lane;
+                    vj[u][e] = d < hd ? to_f32(vr[d]) : 0.f;
+                }
             }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int e = 0; e < NE; ++e) o[e] = fmaf(pj[u], vj[u][e], o[e]);
         }
         m = m_new;
     }
@@ -234,7 +246,7 @@ static int launch(const void* q, int q_stride, void* out, int out_stride, const 
 }
 
 // scratch (may be null) and max_chunks: with scratch of n_tokens * nq * max_chunks * (hd + 2) floats and
-// max_chunks > 1 the split kernels run; max_chunks must be at least the number of chunks of 256 keys that any
+// max_chunks > 1 the split kernels run; max_chunks must be at least the number of chunks of 64 keys that any
 // row of the step touches, or the results, still right, are no longer bit-equal to the walk's.
 WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                        const void* v_pages, int dtype, const int* token_req, const int* positions,

@@ -45,12 +45,15 @@ WLLM_API int wllm_stage_send(const void* pinned, void* staged, void* dst, long l
 
 // `bytes` from `src` (device) to `pinned`, on the copy stream, behind everything the step's stream holds now:
 // `queued` is recorded on the step's stream and awaited by the copy stream; `done` is recorded behind the copy.
-WLLM_API int wllm_stage_fetch(void* pinned, const void* src, long long bytes, cudaStream_t step_stream,
-                              cudaStream_t copy_stream, void* queued, void* done) {
+// `extra_bytes` from `extra` (device; the kernels' status word) land right behind them in `pinned`.
+WLLM_API int wllm_stage_fetch(void* pinned, const void* src, long long bytes, const void* extra, long long extra_bytes,
+                              cudaStream_t step_stream, cudaStream_t copy_stream, void* queued, void* done) {
     if (bytes <= 0) return WLLM_OK;
     cudaError_t e = cudaEventRecord((cudaEvent_t)queued, step_stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(copy_stream, (cudaEvent_t)queued, 0);
     if (e == cudaSuccess) e = cudaMemcpyAsync(pinned, src, (size_t)bytes, cudaMemcpyDeviceToHost, copy_stream);
+    if (e == cudaSuccess && extra != nullptr && extra_bytes > 0)
+        e = cudaMemcpyAsync((char*)pinned + bytes, extra, (size_t)extra_bytes, cudaMemcpyDeviceToHost, copy_stream);
     if (e == cudaSuccess) e = cudaEventRecord((cudaEvent_t)done, copy_stream);
     return status_of(e);
 }

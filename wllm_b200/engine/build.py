@@ -39,9 +39,11 @@ def build_model(folder: str | None, dtype, device, config=None, random_seed: int
     return model
 
 
-def build_runner(model: ComposedModel, engine: EngineConfig, num_pages: int | None = None) -> ModelRunner:
+def build_runner(model: ComposedModel, engine: EngineConfig, num_pages: int | None = None,
+                 poison_pages: bool = False) -> ModelRunner:
     device = require_cuda(engine.device)
     cache = CacheManager(model.group_specs, page_size=engine.block_size,
                          num_pages=num_pages if num_pages is not None else engine.num_blocks,
-                         max_requests=engine.max_num_seqs, states=model.state_specs, dtype=model.dtype, device=device)
+                         max_requests=engine.max_num_seqs, states=model.state_specs, dtype=model.dtype, device=device,
+                         poison=poison_pages)
     return ModelRunner(model, cache, device)

@@ -24,6 +24,8 @@ class ComposedModel:
         self.final_norm = NORMS.build(plan.final_norm, **kw)
         self.head = LogitsHead(plan.head, embedding=self.embedding, **kw)
         self.group_specs, self.state_specs, self.cache_refs = self._assign_caches()
+        # captured decode steps replay launches and run a step twice when they are captured (see parts/base.py)
+        self.graph_safe = not self.state_specs and all(getattr(p, "graph_safe", False) for p in self.parts() + self.blocks)
         self.loaded = False
 
     def _assign_caches(self):

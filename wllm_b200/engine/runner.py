@@ -67,7 +67,7 @@ class StepContext:
         others to the tiled prefill kernel; both find their requests by q_len on the device."""
         ps = self.cache.page_size
         if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
-            # few rows over long contexts (decoding): a warp per chunk of 256 keys instead of a warp per row
+            # few rows over long contexts (decoding): a warp per chunk of 64 keys instead of a warp per row
             rows, chunks = q.shape[0] * nq, ops.simt_chunks(self.max_ctx, window)
             scratch = None
             if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
@@ -305,14 +305,16 @@ class ModelRunner:
     # -- captured decode steps -------------------------------------------------------------
     def enable_graphs(self) -> None:
         """Replay a captured CUDA graph for steps in which every request brings one token and
-        wants its logits (a decode step).  One graph per (number of requests, table width);
+        wants its logits (a decode step), if every part of the model is `graph_safe` and none keeps
+        per-request state; other models step eagerly.  One graph per (number of requests, table width);
         the index arrays live at fixed device addresses and are rewritten before each replay.
         The reference captures its decode step in batch-size buckets the same way
         (src/wllm/engine/cuda_graph_decoder.py:34-178)."""
         self._graphs_on = True
 
     def _graphable(self, entries: list) -> bool:
-        return self._graphs_on and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        return self._graphs_on and self.model.graph_safe and \
+            all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
     def _forward_graph(self, entries: list, device_tokens=None) -> torch.Tensor:
         widest = max(1, max(len(t) for e in entries for t in e.cache.tables))

@@ -159,7 +159,7 @@ class Scheduler:
             budget -= c
             plan.append((r, r.num_computed, c))
         for r, _, c in plan:
-            taken += self.cache.pages_needed([(r.cache, c)])[0] if self.cache.groups else 0
+            taken += max(self.cache.pages_needed([(r.cache, c)]), default=0)     # of the group that needs most
         while self.waiting and budget > 0:
             r = self.waiting[0]
             if not self._may_admit(r, taken):

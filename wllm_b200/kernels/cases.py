@@ -103,7 +103,7 @@ def gemm_f32(args) -> None:
 
 
 def attention_f32(args) -> None:
-    """The 32-bit attention (one warp per row, or per row and chunk of 256 keys) as a step context would call it."""
+    """The 32-bit attention (one warp per row, or per row and chunk of 64 keys) as a step context would call it."""
     nq, nkv, hd, ps = args.heads, args.kv_heads, args.head_dim, args.page_size
     R, ctx, q_len = args.requests, args.context, args.tokens
     pages_each = -(-ctx // ps)

@@ -148,11 +148,11 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
            "rope_kv_write")
 
 
-SIMT_CHUNK = 256   # keys per chunk of the one-warp-per-row attention (csrc/attention_simt.cu)
+SIMT_CHUNK = 64    # keys per chunk of the one-warp-per-row attention (csrc/attention_simt.cu)
 
 
 def simt_chunks(max_ctx: int, window: int) -> int:
-    """Upper bound of the chunks of 256 keys that a row of a step touches, from the longest context of the
+    """Upper bound of the chunks of 64 keys that a row of a step touches, from the longest context of the
     step (and the window, if the layer has one)."""
     most = -(-max(1, max_ctx) // SIMT_CHUNK)
     return min(most, -(-window // SIMT_CHUNK) + 1) if window > 0 else most
@@ -164,7 +164,7 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
                          scratch: torch.Tensor | None = None, max_chunks: int = 0) -> torch.Tensor:
     """q: [n, nq*hd] view (row stride free); pages: [num_pages, nkv, page_size, hd]; out: [n, nq*hd].
     With `scratch` (float32, n * nq * max_chunks * (hd + 2) floats) and max_chunks = simt_chunks(...) > 1 every
-    (row, chunk of 256 keys) gets a warp of its own and a second kernel merges them; the result is the same,
+    (row, chunk of 64 keys) gets a warp of its own and a second kernel merges them; the result is the same,
     bit for bit, as without."""
     _need_cuda(q, out, k_pages, v_pages, token_req, positions, block_table, scratch)
     n = q.shape[0]
@@ -186,8 +186,16 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
     return out
 
 
+def _indexed(device) -> torch.device:
+    device = torch.device(device)
+    if device.index is None and device.type == "cuda":
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
+
+
 def _status_word(device) -> torch.Tensor:
-    """One int32 per device that stays 0 unless a kernel's bounded wait ran out (see kernel_status)."""
+    """One int32 per device that stays 0 unless a kernel's bounded wait ran out (see tc_gemm_status)."""
+    device = _indexed(device)
     status = _tc_status.get(device)
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=device)
@@ -436,10 +444,22 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     return out
 
 
+GAVE_UP = {11: "GEMM producer", 12: "GEMM tensor-core issue", 13: "GEMM epilogue", 21: "decode attention",
+           22: "prefill attention (mma)", 23: "prefill attention loads", 24: "prefill attention tensor-core issue",
+           25: "prefill attention softmax"}
+
+
 def tc_gemm_status(device) -> int:
-    """0, or the code of a role of the tensor-memory GEMM that gave up waiting (synchronises)."""
-    status = _tc_status.get(torch.device(device))
+    """0, or the code of a role of the tensor-memory GEMM or attention kernels that gave up waiting
+    (synchronises; the engine reads the same word with every step's sampled ids instead)."""
+    status = _tc_status.get(_indexed(device))
     return 0 if status is None else int(status.item())
+
+
+def reset_kernel_status(device) -> None:
+    status = _tc_status.get(_indexed(device))
+    if status is not None:
+        status.zero_()
 
 
 TC_MIN_ROWS = 65   # below this a step is bound by streaming the weights; see linear()

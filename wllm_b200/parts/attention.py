@@ -22,6 +22,7 @@ from .base import MIXERS, POSITIONS, CacheRef, KVNeed, ParamSpec, as_branch
 
 @MIXERS.register("attention")
 class PagedAttention:
+    graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.nq, self.nkv, self.hd = int(spec.num_heads), int(spec.num_kv_heads), int(spec.head_dim)
         if self.nq % self.nkv:

@@ -23,6 +23,12 @@ Interfaces (duck-typed; see the built-in parts for examples):
                     __call__(x, ctx, cache: CacheRef) -> tensor [n, hidden]
     feed-forward    __call__(x, ctx) -> tensor [n, hidden]
     block           __call__(residual, ctx, cache: CacheRef) -> None (updates the residual)
+
+A part may declare `graph_safe = True`: everything it launches depends on device data and on the step's
+size bounds alone (tokens, requests, table width, longest context rounded to the table's reach), never on
+host copies of the batch's contents, and running the same step twice leaves the same cache and state.  Decode
+steps are replayed from captured CUDA graphs only for models whose parts all say so and that declare no
+per-request state; any other model runs every step eagerly, whatever `cuda_graphs` asks for.
 """
 from __future__ import annotations
 

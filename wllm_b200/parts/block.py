@@ -14,6 +14,7 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheRef, Residual
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock:
+    graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype):
         kw = dict(hidden_size=hidden_size, model_dtype=model_dtype)
         self.norm_in = NORMS.build(spec.norm_in, **kw)

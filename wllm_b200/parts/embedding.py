@@ -18,6 +18,7 @@ from .base import ParamSpec
 
 
 class ScaledEmbedding:
+    graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.weight_name, self.vocab = spec.weight, int(spec.vocab_size)
         self.hidden_size, self.model_dtype = hidden_size, model_dtype
@@ -41,6 +42,7 @@ class ScaledEmbedding:
 
 
 class LogitsHead:
+    graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype, embedding: ScaledEmbedding):
         self.tied = bool(spec.tied)
         self.vocab = int(spec.vocab_size)

@@ -16,6 +16,7 @@ from .base import FEED_FORWARDS, ParamSpec, as_branch
 
 @FEED_FORWARDS.register("gated_dense")
 class GatedDense:
+    graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.inter = int(spec.intermediate_size)
         self.activation = spec.activation

@@ -15,6 +15,7 @@ from .base import NORMS, ParamSpec, Residual
 
 @NORMS.register("rmsnorm")
 class RMSNorm:
+    graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
         self.weight_name = spec.weight
         self.eps = float(spec.eps)

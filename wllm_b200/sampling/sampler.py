@@ -28,9 +28,16 @@ class PendingSample:
         self._owner = owner          # the sampler (and with it the event) lives as long as its results are awaited
 
     def get(self):
+        """(tokens, log-probabilities).  The kernels' status word came along with them: if a bounded wait in one
+        of the step's kernels ran out, its results are partial, and the tokens are not handed on."""
         if self.rows == 0:
             return [], []
         ops._check(self._lib.wllm_event_wait(self._done), "waiting for the sampled ids")
+        status = int(self._host[2 * self.rows])
+        if status != 0:
+            ops.reset_kernel_status(self._owner.device)
+            raise ops.KernelError(f"a kernel of this step gave up waiting (status {status}: "
+                                  f"{ops.GAVE_UP.get(status, 'unknown role')}); its tokens are not used")
         out = self._host[:2 * self.rows]
         return out[:self.rows].tolist(), out[self.rows:].view(np.float32).tolist()
 
@@ -77,15 +84,16 @@ class Sampler:
         tokens = self.launch(logits, params, counters, seeds, generated)
         self._turn ^= 1
         host = self._out_hosts[self._turn]
-        if host is None or host[0].numel() < 2 * rows:
-            pinned = torch.empty(max(2 * rows, 1024), dtype=torch.int32).pin_memory()
+        if host is None or host[0].numel() < 2 * rows + 1:
+            pinned = torch.empty(max(2 * rows + 1, 1024), dtype=torch.int32).pin_memory()
             host = self._out_hosts[self._turn] = (pinned, pinned.numpy())
         done = self._done[self._turn]
         # the copy to the host runs on a stream of its own and leaves the step's stream free for the next step's first kernels
         ops._check(lib.wllm_stage_fetch(c_void_p(host[0].data_ptr()), c_void_p(self._out.data_ptr()), c_longlong(8 * rows),
+                                        c_void_p(ops._status_word(self.device).data_ptr()), c_longlong(4),
                                         ops._stream(), self._side_raw, self._queued, done), "copy of the sampled ids")
         self._read = done
-        self.d2h_bytes = 8 * rows
+        self.d2h_bytes = 8 * rows + 4
         return PendingSample(rows, tokens, host[1], done, lib, self)
 
     def _scratch_for(self, rows: int, lib) -> c_void_p:
