@@ -69,7 +69,7 @@ def paged_attention(q, out, k_pages, v_pages, token_req, positions, block_table,
     for t in range(n):
         pos, table = int(positions[t]), block_table[int(token_req[t])]
         first = max(0, pos - window + 1) if window > 0 else 0
-        keys = torch.arange(first, pos + 1)
+        keys = torch.arange(first, pos + 1, device=k_pages.device)
         pages = table[(keys // page_size).long()].long()
         offs = (keys % page_size).long()
         k = k_pages[pages, :, offs, :].to(dtype)   # [keys, nkv, hd]

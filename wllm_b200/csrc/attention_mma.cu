@@ -90,6 +90,21 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Rows [row_lo, row_hi) of a value tile of ROWS rows in the box-copy layout (`blocks` column blocks of
+// [ROWS][128 bytes]) set to zero, by `nthreads` threads of which this is number `tid`.  A box copy brings whole
+// rows of a page: behind a request's last key, and in front of a window's first, they hold whatever the page
+// holds.  Such keys get a weight of zero, but the product 0 x v is no zero when v is not a number, so their
+// values are cleared in the few tiles that reach past either end.
+template <int ROWS>
+__device__ __forceinline__ void zero_value_rows(uint32_t v_tile, int blocks, int row_lo, int row_hi, int tid, int nthreads) {
+    const int per_row = blocks * 8;
+    for (int i = tid; i < (row_hi - row_lo) * per_row; i += nthreads) {
+        const int row = row_lo + i / per_row, rest = i % per_row;
+        const uint32_t addr = v_tile + (rest >> 3) * (ROWS * 128) + row * 128 + (rest & 7) * 16;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+    }
+}
+
 // One 64-key tile of keys AND values of kv head `g` into shared memory (all threads of the CTA).
 // Each warp first reads the tile's page ids (at most four pages of 16 keys) with one load and hands
 // them out by shuffle, so the copies that follow depend on no further load.
@@ -258,6 +273,7 @@ struct TileRing {
     const CUtensorMap *k_map, *v_map;
     const int* table;
     int max_pages, key_lo, key_hi, g, nkv, page_size, page_shift, t0, t1;
+    int ctx_end;                  // the request's keys end here: rows of a box copy from here on hold no key
 
     __device__ __forceinline__ uint32_t k_stage(int s) const { return kv_s + (2 * s) * TILE_BYTES; }
     __device__ __forceinline__ uint32_t v_stage(int s) const { return kv_s + (2 * s + 1) * TILE_BYTES; }
@@ -294,6 +310,10 @@ struct TileRing {
         if (USE_TMA) {
             const int n = t - t0;
             ok = mbar_wait(bars + 8 * (n % STAGES), (n / STAGES) & 1) ? 1 : 0;
+            if (ok && t * BN + BN > ctx_end)
+                zero_value_rows<BN>(v_stage(n % STAGES), HD / 64, max(0, ctx_end - t * BN), BN, threadIdx.x, NT);
+            if (ok && t * BN < key_lo)
+                zero_value_rows<BN>(v_stage(n % STAGES), HD / 64, 0, min(BN, key_lo - t * BN), threadIdx.x, NT);
         } else {
             cp_wait<STAGES - 2>();
         }
@@ -373,6 +393,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     ring.key_lo = key_lo; ring.key_hi = key_hi; ring.g = g; ring.nkv = nkv; ring.page_size = page_size;
     ring.page_shift = 31 - __clz(page_size);
     ring.t0 = key_lo / BN; ring.t1 = empty ? ring.t0 : (key_hi + BN - 1) / BN;
+    ring.ctx_end = ctx;
     ring.init();
     load_q_tile<NTHREADS, 16>(q_s, q, q_stride, token, 1, 0, 16, g, rep);
     if (USE_TMA) cp_commit();
@@ -569,6 +590,14 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
             if (!mbar_wait(full0 + 8 * s, (n / WS_STAGES) & 1)) { ok = false; break; }
             __syncwarp();
             const uint32_t k_src = base + (2 * s) * WS_TILE_BYTES;
+            const int tile_start = (t0 + n) * WS_BN;
+            if (tile_start + WS_BN > ctx || tile_start < key_lo) {      // rows that hold no key of this request
+                if (tile_start + WS_BN > ctx)
+                    zero_value_rows<WS_BN>(k_src + WS_TILE_BYTES, HD / 64, max(0, ctx - tile_start), WS_BN, lane, 32);
+                if (tile_start < key_lo)
+                    zero_value_rows<WS_BN>(k_src + WS_TILE_BYTES, HD / 64, 0, min(WS_BN, key_lo - tile_start), lane, 32);
+                __syncwarp();
+            }
             warp_tile<WS_BN, 16, WS_BN>(st, q_s, 0, k_src, k_src + WS_TILE_BYTES, 0, (t0 + n) * WS_BN, hi_r, first_r, scale2);
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * s) : "memory");
@@ -741,6 +770,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     ring.key_lo = key_lo; ring.key_hi = key_hi; ring.g = g; ring.nkv = nkv; ring.page_size = page_size;
     ring.page_shift = 31 - __clz(page_size);
     ring.t0 = key_lo / BN; ring.t1 = (key_hi + BN - 1) / BN;
+    ring.ctx_end = ctx;
     ring.init();
     load_q_tile<PRE_THREADS, BM>(q_s, q, q_stride, q_start, q_len, row0, BM, g, rep);
     if (USE_TMA) cp_commit();

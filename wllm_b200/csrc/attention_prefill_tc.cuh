@@ -254,6 +254,17 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             m_run = m_new;
             // P over the scores this thread has just read: keys (2j, 2j + 1) in column j of the buffer
             tc_st32(t_lane + TC_S_COL + b * TC_BN, packed);
+            if (key0 + TC_BN > ctx || key0 < key_lo) {
+                // The value tile reaches past the request's last key (or in front of the window's first): those rows
+                // hold whatever the page holds, and a weight of zero times something that is no number is no zero.
+                // They are cleared before this warp reports P, which is what the output product waits for.
+                const int vs = n % TC_KV_STAGES;
+                if (!mbar_wait(v_full + 8 * vs, (n / TC_KV_STAGES) & 1)) { ok = false; break; }
+                const uint32_t vt = v_s + vs * TC_KV_BYTES;
+                if (key0 + TC_BN > ctx) zero_value_rows<TC_BN>(vt, HD / 64, max(0, ctx - key0), TC_BN, threadIdx.x - 64, 128);
+                if (key0 < key_lo) zero_value_rows<TC_BN>(vt, HD / 64, 0, min(TC_BN, key_lo - key0), threadIdx.x - 64, 128);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
             if (n > 0) {
                 if (!mbar_wait(pv_done, (n - 1) & 1)) { ok = false; break; }     // O of the tile before is complete
                 tc_fence_after();
@@ -420,6 +431,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
     const uint32_t k_full = bars, k_empty = k_full + 8 * PR_STAGES, v_full = k_empty + 8 * PR_STAGES;
     const uint32_t v_empty = v_full + 8 * PR_STAGES, s_full = v_empty + 8 * PR_STAGES;
     const uint32_t q_full = s_full + 16, p_full = q_full + 8, pv_done = p_full + 8, tmem_slot = pv_done + 8;
+    const uint32_t v_edge = tmem_slot + 8;          // this CTA's own: the value tiles that need clearing land on it
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     // the keys that the pair's 256 rows see
@@ -439,6 +451,7 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
         mbar_init(q_full, 8);
         mbar_init(p_full, 8);
         mbar_init(pv_done, 1);
+        mbar_init(v_edge, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -462,19 +475,36 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
             const int row_lo = kv ? 0 : 64 * (int)rank, row_n = kv ? PR_BN : 64;
             const int col_lo = kv ? (HD / 2) * (int)rank : 0, col_blocks = kv ? HD / 128 : HD / 64;
             bool ok = true;
-            int n = 0;
+            int n = 0, edges = 0;
             for (; n < T && ok; ++n) {
                 const int s = n % PR_STAGES, ph = (n / PR_STAGES) & 1, tile_start = (t0 + n) * PR_BN + row_lo;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { ok = false; break; }
                 const uint32_t bar = full0 + 8 * s, dst = ring + s * stage_bytes;
-                mbar_expect_tx_cluster(bar, stage_bytes);
+                // A value tile that reaches past the request's last key (or in front of the window's first) holds, in
+                // those rows, whatever the page holds; their weight is zero, but zero times something that is no
+                // number is no zero.  Such a tile (the last of a request's last rows) lands on a barrier of this CTA's
+                // own, its stray rows are cleared, and only then is it announced on the pair's barrier, by a plain
+                // arrival in place of the byte count.
+                const int key0 = (t0 + n) * PR_BN;
+                const bool edge = kv && (key0 + PR_BN > ctx || key0 < key_lo);
+                if (edge) mbar_expect_tx(v_edge, stage_bytes); else mbar_expect_tx_cluster(bar, stage_bytes);
                 for (int r0 = 0; r0 < row_n; r0 += box_rows) {
                     const int key = tile_start + r0, index = key >> page_shift;
                     int page = index < max_pages ? table[index] : 0;
                     if (page < 0) page = 0;
                     const int row = (page * nkv + g) * page_size + (key & (page_size - 1));
-                    for (int cb = 0; cb < col_blocks; ++cb)
-                        tma_load_2d_pair(dst + cb * (row_n * 128) + r0 * 128, map, bar, col_lo + cb * 64, row);
+                    for (int cb = 0; cb < col_blocks; ++cb) {
+                        if (edge) tma_load_2d(dst + cb * (row_n * 128) + r0 * 128, map, v_edge, col_lo + cb * 64, row);
+                        else tma_load_2d_pair(dst + cb * (row_n * 128) + r0 * 128, map, bar, col_lo + cb * 64, row);
+                    }
+                }
+                if (edge) {
+                    if (!mbar_wait(v_edge, edges & 1)) { ok = false; break; }
+                    ++edges;
+                    if (key0 + PR_BN > ctx) zero_value_rows<PR_BN>(dst, HD / 128, max(0, ctx - key0), PR_BN, 0, 1);
+                    if (key0 < key_lo) zero_value_rows<PR_BN>(dst, HD / 128, 0, min(PR_BN, key_lo - key0), 0, 1);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_arrive_cluster_release(bar);
                 }
             }
             for (int k = 0; k < PR_STAGES && ok; ++k, ++n) {          // nothing in flight at the exit

@@ -155,6 +155,10 @@ __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uin
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// The rare arrival that announces what this thread wrote itself with ordinary stores: released at cluster scope.
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 // Box copy into this CTA's shared memory whose bytes are counted on a barrier that may lie in the other CTA
 // of the pair (`cluster_bar` is a shared::cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y) {
