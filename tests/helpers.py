@@ -38,9 +38,17 @@ def plain_rows(folder: str, name: str, requests: dict) -> dict:
     return rows
 
 
+class HostRing:
+    """Stands in for the engine's ring of pinned staging buffers when a runner is put on the CPU for a test:
+    the index arrays go to their place with a plain copy."""
+
+    def send(self, host, dst) -> None:
+        dst[:host.shape[0]].copy_(torch.from_numpy(host))
+
+
 def host_runner(folder: str, dtype, page_size: int, num_pages: int, max_requests: int = 8):
     """A runner on the CPU for host-logic tests; the kernels must be replaced by
-    kernel_refs.install(monkeypatch) first."""
+    kernel_refs.install(monkeypatch) first, and the staging ring by a plain copy."""
     from wllm_b200.cache import CacheManager
     from wllm_b200.config import config_from_folder
     from wllm_b200.engine import ComposedModel, ModelRunner
@@ -49,7 +57,9 @@ def host_runner(folder: str, dtype, page_size: int, num_pages: int, max_requests
     model = ComposedModel(arch.make_plan(cfg), dtype)
     load_weights(model, folder, "cpu")
     cache = CacheManager(model.group_specs, page_size, num_pages, max_requests, model.state_specs, dtype, "cpu")
-    return ModelRunner(model, cache, "cpu")
+    runner = ModelRunner(model, cache, "cpu")
+    runner._ring = HostRing()
+    return runner
 
 
 def max_diff(rows: dict, ref: dict) -> float:

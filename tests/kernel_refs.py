@@ -34,7 +34,8 @@ def rmsnorm(resid, delta, weight, eps, offset, out, rows=None, delta_splits=0):
     return out
 
 
-def rope_kv_write(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages, nq, nkv, hd, rot_dim, page_size, in_splits=0):
+def rope_kv_write(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages, nq, nkv, hd, rot_dim, page_size, in_splits=0,
+                  pairing="half"):
     if in_splits:
         total = torch.zeros_like(qkv[0])
         for part in qkv:
@@ -46,9 +47,14 @@ def rope_kv_write(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages, nq, 
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
     half = rot_dim // 2
     qk = x[:, : nq + nkv, :]
-    x1, x2 = qk[..., :half].clone(), qk[..., half:rot_dim].clone()
-    qk[..., :half] = x1 * cos - x2 * sin
-    qk[..., half:rot_dim] = x2 * cos + x1 * sin
+    if pairing == "interleaved":      # element 2j turns with 2j + 1
+        x1, x2 = qk[..., 0:rot_dim:2].clone(), qk[..., 1:rot_dim:2].clone()
+        qk[..., 0:rot_dim:2] = x1 * cos - x2 * sin
+        qk[..., 1:rot_dim:2] = x2 * cos + x1 * sin
+    else:                             # element j turns with j + rot_dim/2
+        x1, x2 = qk[..., :half].clone(), qk[..., half:rot_dim].clone()
+        qk[..., :half] = x1 * cos - x2 * sin
+        qk[..., half:rot_dim] = x2 * cos + x1 * sin
     rounded = x.to(q_out.dtype)
     q_out.copy_(rounded[:, :nq].reshape(n, -1))
     if slots is None:

@@ -73,8 +73,9 @@ def test_rmsnorm_32bit_weight_under_bfloat16_output():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing", ["half", "interleaved"])
 @pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(4, 1, 32, 32, 16), (3, 3, 48, 48, 32), (6, 2, 80, 40, 16), (8, 1, 256, 256, 64)])
-def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
+def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps, pairing):
     g = torch.Generator().manual_seed(3)
     n, pages = 21, 9
     qkv = torch.randn(n, (nq + 2 * nkv) * hd, generator=g).to(dtype)
@@ -86,10 +87,10 @@ def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
     k_ref = torch.zeros(pages, nkv, ps, hd, dtype=dtype)
     v_ref = torch.zeros_like(k_ref)
     q_ref = torch.zeros(n, nq * hd, dtype=dtype)
-    ref.rope_kv_write(qkv, q_ref, positions, slots, inv_freq, k_ref, v_ref, nq, nkv, hd, rot, ps)
+    ref.rope_kv_write(qkv, q_ref, positions, slots, inv_freq, k_ref, v_ref, nq, nkv, hd, rot, ps, pairing=pairing)
     q_dev, k_dev, v_dev = (torch.zeros_like(t, device=DEV) for t in (q_ref, k_ref, v_ref))
     ops().rope_kv_write(qkv.to(DEV), q_dev, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k_dev, v_dev, nq, nkv, hd,
-                        rot, ps)
+                        rot, ps, pairing=pairing)
     t = dict(rtol=1e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
     torch.testing.assert_close(q_dev.cpu().float(), q_ref.float(), **t)
     torch.testing.assert_close(k_dev.cpu().float(), k_ref.float(), **t)
@@ -102,10 +103,10 @@ def test_rope_kv_write(dtype, nq, nkv, hd, rot, ps):
     parts = torch.randn(3, *qkv.shape, generator=g)
     whole = (parts[0] + parts[1]) + parts[2]
     q3, k3, v3 = (torch.zeros_like(t) for t in (q_ref, k_ref, v_ref))
-    ref.rope_kv_write(whole.to(dtype).float() if False else whole, q3, positions, slots, inv_freq, k3, v3, nq, nkv, hd, rot, ps)
+    ref.rope_kv_write(whole, q3, positions, slots, inv_freq, k3, v3, nq, nkv, hd, rot, ps, pairing=pairing)
     q3d, k3d, v3d = (torch.zeros_like(t, device=DEV) for t in (q_ref, k_ref, v_ref))
     ops().rope_kv_write(parts.to(DEV), q3d, positions.to(DEV), slots.to(DEV), inv_freq.to(DEV), k3d, v3d, nq, nkv, hd, rot,
-                        ps, in_splits=3)
+                        ps, in_splits=3, pairing=pairing)
     torch.testing.assert_close(q3d.cpu().float(), q3.float(), **t)
     torch.testing.assert_close(k3d.cpu().float(), k3.float(), **t)
     torch.testing.assert_close(v3d.cpu().float(), v3.float(), **t)

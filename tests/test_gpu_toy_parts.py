@@ -1,7 +1,9 @@
-"""Two more kinds of part that the framework has never seen, registered from here: a feed-forward
-with routing (each token goes through the one expert its router picks, router logits in 32-bit)
-and another position encoding (rotary with positions divided by a factor, which the attention
-mixer takes through the same interface as the built-in one).  A toy architecture made of them,
+"""More kinds of part that the framework has never seen, registered from here: a feed-forward
+with routing (each token goes through the one expert its router picks, router logits in 32-bit),
+another position encoding (rotary with positions divided by a factor and neighbouring elements
+turning together, which the attention mixer takes through the same interface as the built-in
+one), an embedding that adds a learned vector per absolute position, and a head that caps its
+logits with a tanh.  A toy architecture made of them,
 with the two kinds of feed-forward alternating by layer, is written to a folder by the
 random-weights mode, loaded and stepped under every way of cutting; the logits are compared with
 a plain whole-sequence statement of the same toy, and in 32-bit with each other bit for bit.
@@ -17,14 +19,16 @@ from helpers import folder_weights, max_diff
 from wllm_b200.config import register_architecture
 from wllm_b200.config.base import ConfigReader
 from wllm_b200.kernels import ops
-from wllm_b200.parts import FEED_FORWARDS, POSITIONS, LayerRun, ModelPlan, ParamSpec, spec
+from wllm_b200.parts import EMBEDDINGS, FEED_FORWARDS, HEADS, POSITIONS, LayerRun, ModelPlan, ParamSpec, spec
 
 pytestmark = pytest.mark.gpu
 
 
 @POSITIONS.register("rope_stretched")
 class StretchedRotary:
-    """Rotary angles of position / factor: the mixer reads `inv_freq` and `rotary_dim`, nothing else."""
+    """Rotary angles of position / factor, elements 2j and 2j + 1 turning together: the mixer reads `inv_freq`,
+    `rotary_dim` and `pairing`, nothing else."""
+    pairing = "interleaved"
 
     def __init__(self, spec, device=None):
         self.rotary_dim = int(spec.head_dim)
@@ -34,6 +38,44 @@ class StretchedRotary:
     def to(self, device):
         self.inv_freq = self.inv_freq.to(device)
         return self
+
+
+@EMBEDDINGS.register("toy_positioned_embedding")
+class PositionedEmbedding:
+    """x[t] = E[id[t]] + P[position[t]]: a learned vector per absolute position, beside the token's."""
+
+    def __init__(self, spec, hidden_size, model_dtype):
+        self.names, self.vocab, self.places = (spec.weight, spec.position_weight), int(spec.vocab_size), int(spec.max_positions)
+        self.hidden_size, self.table, self.places_table = hidden_size, None, None
+
+    def param_specs(self):
+        return [ParamSpec(self.names[0], (self.vocab, self.hidden_size), "table"),
+                ParamSpec(self.names[1], (self.places, self.hidden_size), "table")]
+
+    def load(self, fetch):
+        self.table, self.places_table = fetch(self.names[0]).contiguous(), fetch(self.names[1]).contiguous()
+
+    def __call__(self, token_ids, ctx):
+        out = ctx.buffer("residual", (token_ids.shape[0], self.hidden_size), torch.float32)
+        ops.embed_gather(token_ids, self.table, 1.0, out)
+        return out.add_(self.places_table[ctx.positions.long()].float())
+
+
+@HEADS.register("toy_capped_head")
+class CappedHead:
+    """logits = cap * tanh(h E^T / cap), with the embedding's table."""
+
+    def __init__(self, spec, hidden_size, model_dtype, embedding):
+        self.cap, self.embedding = float(spec.cap), embedding
+
+    def param_specs(self):
+        return []
+
+    def load(self, fetch):
+        pass
+
+    def __call__(self, hidden_rows, ctx):
+        return self.cap * torch.tanh(ops.linear(hidden_rows, self.embedding.table, f32_out=True) / self.cap)
 
 
 @FEED_FORWARDS.register("toy_routed")
@@ -84,6 +126,7 @@ class ToyRoutedConfig:
     eps: float
     theta: float
     stretch: float
+    cap: float
     max_positions: int
     architecture = "ToyRoutedForCausalLM"
 
@@ -92,7 +135,7 @@ class ToyRoutedConfig:
         r = ConfigReader(raw, where)
         cfg = cls(*(r.integer(k) for k in ("vocab_size", "hidden_size", "intermediate_size", "num_layers", "num_heads",
                                            "num_kv_heads", "head_dim", "experts")),
-                  r.number("eps"), r.number("theta"), r.number("stretch"), r.integer("max_positions"))
+                  r.number("eps"), r.number("theta"), r.number("stretch"), r.number("cap"), r.integer("max_positions"))
         r.finish()
         return cfg
 
@@ -118,29 +161,36 @@ def toy_routed_plan(c):
         return spec("pre_norm", norm_in=norm(p + "norm_in.weight"), mixer=attention, norm_post=norm(p + "norm_post.weight"),
                     feed_forward=ffn)
     return ModelPlan(hidden_size=c.hidden_size, vocab_size=c.vocab_size, max_positions=c.max_positions,
-                     embedding=spec("scaled_embedding", weight="embed.weight", vocab_size=c.vocab_size, scale=1.0),
+                     embedding=spec("toy_positioned_embedding", weight="embed.weight", position_weight="places.weight",
+                                    vocab_size=c.vocab_size, max_positions=c.max_positions),
                      blocks=[block(i) for i in range(c.num_layers)], final_norm=norm("final_norm.weight"),
-                     head=spec("logits_head", tied=True, weight="embed.weight", vocab_size=c.vocab_size),
+                     head=spec("toy_capped_head", cap=c.cap),
                      runs=[LayerRun(i) for i in range(c.num_layers)])
 
 
 TOY = dict(architectures=["ToyRoutedForCausalLM"], vocab_size=200, hidden_size=64, intermediate_size=96, num_layers=3,
-           num_heads=4, num_kv_heads=4, head_dim=16, experts=3, eps=1e-6, theta=50.0, stretch=4.0, max_positions=256)
+           num_heads=4, num_kv_heads=4, head_dim=16, experts=3, eps=1e-6, theta=50.0, stretch=4.0, cap=2.0, max_positions=256)
 
 
 # -- the same toy, plainly: whole sequences, no cache -------------------------------------------
 def plain_toy(ids, w, c):
     def norm(x, name):
         return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + c.eps) * (1.0 + w[name])
+    def turn(x):        # elements 2j and 2j + 1 of every head turn together
+        y = torch.empty_like(x)
+        x1, x2 = x[..., 0::2], x[..., 1::2]
+        y[..., 0::2] = x1 * cos[:, None, :] - x2 * sin[:, None, :]
+        y[..., 1::2] = x2 * cos[:, None, :] + x1 * sin[:, None, :]
+        return y
     T = len(ids)
-    x = w["embed.weight"][torch.as_tensor(ids)]
+    x = w["embed.weight"][torch.as_tensor(ids)] + w["places.weight"][:T]
     margin = torch.full((T,), float("inf"))          # the closest call any router makes on each token
-    cos, sin = plain.rope_tables(torch.arange(T).float() / c.stretch, c.head_dim, c.theta)
+    cos, sin = (t[:, :c.head_dim // 2] for t in plain.rope_tables(torch.arange(T).float() / c.stretch, c.head_dim, c.theta))
     for i in range(c.num_layers):
         p = f"layers.{i}."
         h = norm(x, p + "norm_in.weight")
-        q = plain.apply_rope((h @ w[p + "q.weight"].T).view(T, c.num_heads, c.head_dim), cos, sin)
-        k = plain.apply_rope((h @ w[p + "k.weight"].T).view(T, c.num_kv_heads, c.head_dim), cos, sin)
+        q = turn((h @ w[p + "q.weight"].T).view(T, c.num_heads, c.head_dim))
+        k = turn((h @ w[p + "k.weight"].T).view(T, c.num_kv_heads, c.head_dim))
         v = (h @ w[p + "v.weight"].T).view(T, c.num_kv_heads, c.head_dim)
         x = x + plain.attention(q, k, v).reshape(T, -1) @ w[p + "o.weight"].T
         h = norm(x, p + "norm_post.weight")
@@ -157,7 +207,7 @@ def plain_toy(ids, w, c):
         else:
             gate = torch.nn.functional.gelu(h @ w[p + "gate.weight"].T, approximate="tanh")
             x = x + (gate * (h @ w[p + "up.weight"].T)) @ w[p + "down.weight"].T
-    return norm(x, "final_norm.weight") @ w["embed.weight"].T, margin
+    return c.cap * torch.tanh(norm(x, "final_norm.weight") @ w["embed.weight"].T / c.cap), margin
 
 
 @pytest.fixture(scope="module")
@@ -186,13 +236,15 @@ def test_parts_are_chosen_layer_by_layer(toy):
     kinds = [type(b.feed_forward) for b in model.blocks]
     assert kinds == [ToyRoutedFeedForward, GatedDense, ToyRoutedFeedForward]
     assert all(isinstance(b.mixer.position, StretchedRotary) for b in model.blocks)
+    assert isinstance(model.embedding, PositionedEmbedding) and isinstance(model.head, CappedHead)
+    assert not model.graph_safe          # parts that do not say they may be captured keep the model eager
     names = {p.name for p in model.param_specs()}
     assert "layers.0.moe.experts.2.down.weight" in names and "layers.1.gate.weight" in names
 
 
 def test_the_router_spreads_the_tokens(toy):
     _, reqs, _, w, c, _ = toy
-    x = w["embed.weight"][torch.as_tensor(reqs["r2"])]
+    x = w["embed.weight"][torch.as_tensor(reqs["r2"])] + w["places.weight"][:len(reqs["r2"])]
     h = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + c.eps) * (1.0 + w["layers.0.norm_in.weight"])
     chosen = (h @ w["layers.0.moe.router.weight"].T).argmax(-1)
     assert len(set(chosen.tolist())) == c.experts        # the toy's weights do send tokens to every expert

@@ -4,6 +4,7 @@
 //   angle = float(position) * inv_freq[j],  j < rot_dim/2        (32-bit, sinf/cosf)
 //   y[j]         = x[j] * cos - x[j + rot/2] * sin
 //   y[j + rot/2] = x[j + rot/2] * cos + x[j] * sin                (pairs j, j + rot/2)
+// or, with `interleaved`, the same rotation of the pairs (2j, 2j + 1).
 // Dimensions from rot_dim up to head_dim pass through unrotated.  The rotated queries go to `q_out`
 // [n, nq * hd].  The input row may come as `in_splits` partial sums (slabs `in_split_stride` elements
 // apart, as the split-K matrix product leaves them), which are added in slab order first.  A token
@@ -23,7 +24,7 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
                                      TO* __restrict__ q_out, int q_stride, const int* __restrict__ positions,
                                      const int* __restrict__ slots, const float* __restrict__ inv_freq,
                                      TO* __restrict__ k_pages, TO* __restrict__ v_pages, int nq, int nkv, int hd,
-                                     int rot_dim, int page_size) {
+                                     int rot_dim, int page_size, int interleaved) {
     pdl_launch_dependents();
     const int t = blockIdx.x;
     const int slot = slots ? slots[t] : -1;
@@ -65,9 +66,10 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
         for (int j = threadIdx.x; j < half; j += blockDim.x) {
             float sn = s0, cs = c0;
             if (j != (int)threadIdx.x) sincosf(pos * inv_freq[j], &sn, &cs);
-            const float x1 = in(j), x2 = in(j + half);
-            dst[j] = from_f32<TO>(x1 * cs - x2 * sn);
-            dst[j + half] = from_f32<TO>(x2 * cs + x1 * sn);
+            const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
+            const float x1 = in(ia), x2 = in(ib);
+            dst[ia] = from_f32<TO>(x1 * cs - x2 * sn);
+            dst[ib] = from_f32<TO>(x2 * cs + x1 * sn);
         }
         for (int c = rot_dim + threadIdx.x; c < hd; c += blockDim.x) dst[c] = from_f32<TO>(in(c));
     }
@@ -133,11 +135,11 @@ __global__ void rope_kv_write_rows_kernel(const bf16* __restrict__ qkv, int row_
 WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, int in_splits, long long in_split_stride,
                                 void* q_out, int out_dtype, int q_stride, const int* positions, const int* slots,
                                 const float* inv_freq, void* k_pages, void* v_pages, int n, int nq, int nkv, int hd,
-                                int rot_dim, int page_size, cudaStream_t stream) {
+                                int rot_dim, int page_size, int interleaved, cudaStream_t stream) {
     if (n <= 0) return WLLM_OK;
     if (hd <= 0 || rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || page_size <= 0 || nq <= 0 || nkv <= 0 || in_splits < 1)
         return WLLM_BAD_SIZE;
-    if (n >= 256 && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
+    if (n >= 256 && !interleaved && in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16 && in_splits == 1 && hd % 8 == 0 && rot_dim % 16 == 0 &&
         row_stride % 8 == 0 && q_stride % 8 == 0 && !((uintptr_t)qkv & 15) && !((uintptr_t)q_out & 15) &&
         !((uintptr_t)k_pages & 15) && !((uintptr_t)v_pages & 15))
         return wllm_launch(rope_kv_write_rows_kernel, n, 128, (size_t)rot_dim * sizeof(float), stream, (const bf16*)qkv, row_stride,
@@ -148,7 +150,7 @@ WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, i
     const dim3 grid(n, all_heads ? 1 : nq + 2 * nkv);
 #define GO2(TI, TO, A) wllm_launch(rope_kv_write_kernel<TI, TO, A>, grid, threads, 0, stream, (const TI*)qkv, row_stride, in_splits, \
         (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
-        rot_dim, page_size)
+        rot_dim, page_size, interleaved)
 #define GO(TI, TO) (all_heads ? GO2(TI, TO, true) : GO2(TI, TO, false))
     if (in_dtype == WLLM_BF16 && out_dtype == WLLM_BF16) return GO(bf16, bf16);
     if (in_dtype == WLLM_F32 && out_dtype == WLLM_BF16) return GO(float, bf16);

@@ -11,18 +11,17 @@ from __future__ import annotations
 import torch
 
 from ..cache import CacheGroupSpec, StateSpec
-from ..parts import BLOCKS, NORMS, CacheRef, KVNeed, ModelPlan, Residual, StateNeed
-from ..parts.embedding import LogitsHead, ScaledEmbedding
+from ..parts import BLOCKS, EMBEDDINGS, HEADS, NORMS, CacheRef, KVNeed, ModelPlan, Residual, StateNeed
 
 
 class ComposedModel:
     def __init__(self, plan: ModelPlan, dtype: torch.dtype):
         self.plan, self.dtype = plan, dtype
         kw = dict(hidden_size=plan.hidden_size, model_dtype=dtype)
-        self.embedding = ScaledEmbedding(plan.embedding, **kw)
+        self.embedding = EMBEDDINGS.build(plan.embedding, **kw)
         self.blocks = [BLOCKS.build(b, **kw) for b in plan.blocks]
         self.final_norm = NORMS.build(plan.final_norm, **kw)
-        self.head = LogitsHead(plan.head, embedding=self.embedding, **kw)
+        self.head = HEADS.build(plan.head, embedding=self.embedding, **kw)
         self.group_specs, self.state_specs, self.cache_refs = self._assign_caches()
         # captured decode steps replay launches and run a step twice when they are captured (see parts/base.py)
         self.graph_safe = not self.state_specs and all(getattr(p, "graph_safe", False) for p in self.parts() + self.blocks)

@@ -35,11 +35,10 @@ class StepEntry:
     device_row: int | None = None
 
 
-SM_COUNT = 148   # B200
-
-
 class StepContext:
-    """The batch as the parts see it: index arrays on the device, the cache, scratch buffers."""
+    """The batch as the parts see it: index arrays on the device (and the same on the host, for launch decisions),
+    the cache, scratch buffers, and a few facts about the batch's shape (how many requests bring one token and how
+    many several, the longest portion, the longest context).  It chooses no kernel: that is the parts' business."""
 
     def __init__(self, runner: "ModelRunner"):
         self.runner = runner
@@ -51,7 +50,7 @@ class StepContext:
         self.group_tables: list = []
         self.host = None   # the same arrays on the host, for launch decisions
         self.num_single = self.num_multi = 0     # requests with one token / with several
-        self._share_plans: dict = {}             # prefill attention's tile sharing, by head layout
+        self.memo: dict = {}                     # what a part worked out for this step and wants again in the next layer
         self.max_q_len = self.max_ctx = 0        # bounds that size the attention grids
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
@@ -59,56 +58,6 @@ class StepContext:
 
     def state(self, name: str) -> torch.Tensor:
         return self.cache.slots.tensors[name]
-
-    def attention(self, q, out, k_pages, v_pages, group: int, nq: int, nkv: int, hd: int, window: int, scale: float):
-        """Attention of every token of the step over its request's pages.  float32 (and head sizes the
-        tensor-core kernels are not built for): the one-warp-per-row kernel, whose result does not depend
-        on the batch at all.  bfloat16: requests with one token go to the split-key decode kernel, the
-        others to the tiled prefill kernel; both find their requests by q_len on the device."""
-        ps = self.cache.page_size
-        if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
-            # few rows over long contexts (decoding): a warp per chunk of 64 keys instead of a warp per row
-            rows, chunks = q.shape[0] * nq, ops.simt_chunks(self.max_ctx, window)
-            scratch = None
-            if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
-                scratch = self.buffer("attention_chunks", (rows * chunks * (hd + 2),), torch.float32)
-            ops.paged_attention_simt(q, out, k_pages, v_pages, self.token_req, self.positions,
-                                     self.group_tables[group], nq, nkv, hd, ps, window, scale, scratch, chunks)
-            return
-        table = self.group_tables[group]
-        decode = self.num_single > 0 and nq // nkv <= 16
-        if decode:
-            R = self.n_requests
-            # one CTA fits on an SM: every (request, kv head) is cut into parts so that the CTAs finish together
-            # (planned for the context rounded up to 512 keys, so that a growing context seldom needs a new plan)
-            split_keys, max_splits = ops.decode_split_plan(R * nkv, -(-self.max_ctx // 512) * 512, 32 if hd % 64 == 0 else 64)
-            scratch = self.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
-                                  torch.float32)
-            ops.attention_mma_decode(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,
-                                     table, nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch)
-        if self.num_multi > 0 or not decode:
-            split_above, halves = self._shared_tiles(nq, nkv, hd, skip_single=decode)
-            ops.attention_mma_prefill(q, out, k_pages, v_pages, self.req_q_start, self.req_q_len, self.req_ctx_len,
-                                      table, self.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode,
-                                      split_above=split_above, halves=halves)
-
-    def _shared_tiles(self, nq: int, nkv: int, hd: int, skip_single: bool):
-        """Whether this step's prefill attention shares its heavy tiles between two CTAs (ops.prefill_share_plan),
-        and the buffer for their partial results.  Worked out once a step and head layout, not once a layer;
-        head sizes that run on pairs of CTAs (steps of 128, more than one tile of rows) never share."""
-        key = (nq, nkv, hd, skip_single)
-        if key not in self._share_plans:
-            if hd % 128 == 0 and self.max_q_len * (nq // nkv) > 128:
-                plan = 0
-            else:
-                plan = ops.prefill_share_plan(self.host["req_q_len"].tolist(), self.host["req_ctx_len"].tolist(), nq, nkv,
-                                              hd, skip_single)
-            self._share_plans[key] = plan
-        split_above = self._share_plans[key]
-        if split_above <= 0:
-            return 0, None
-        floats = ops.attention_prefill_halves_floats(self.n_requests, self.max_q_len, nq, nkv, hd)
-        return split_above, self.buffer("attention_halves", (floats,), torch.float32)
 
 
 class ModelRunner:

@@ -46,7 +46,6 @@ def free_events(lib, events) -> None:
 class PinnedRing:
     def __init__(self, device, slots: int = 4):
         self.device = torch.device(device)
-        self.cuda = self.device.type == "cuda"
         self._bufs = [None] * slots         # pinned tensors and numpy views of them
         self._views = [None] * slots
         self._staged = [None] * slots       # device-side staging buffers
@@ -63,9 +62,6 @@ class PinnedRing:
     def send(self, host: np.ndarray, dst: torch.Tensor) -> None:
         """Copy the int32 array `host` into the front of the device tensor `dst`."""
         n = host.shape[0]
-        if not self.cuda:
-            dst[:n].copy_(torch.from_numpy(host))
-            return
         if self._lib is None:
             from ..kernels.build import load_family
             self._lib = load_family("staging")

@@ -24,6 +24,17 @@ from .build import KernelBuildError, load_family
 launches = 0
 
 _F32, _BF16 = 0, 1
+_sms = None
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current CUDA device (148 on a B200); every launch plan below is sized from it.
+    Without a device (the plans are also exercised on the host) the B200's number stands in."""
+    global _sms
+    if _sms is None:
+        _sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+            if torch.cuda.is_available() else 148
+    return _sms
 _STATUS = {1: "element type not supported", 2: "size not supported", 3: "pointer or stride not aligned",
            4: "size beyond the entry point's fixed scratch", 5: "device set-up failed"}
 
@@ -125,9 +136,13 @@ def rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, offset
 
 
 def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor, slots, inv_freq: torch.Tensor,
-                  k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, in_splits: int = 0) -> None:
+                  k_pages, v_pages, nq: int, nkv: int, hd: int, rot_dim: int, page_size: int, in_splits: int = 0,
+                  pairing: str = "half") -> None:
     """Rotate the q and k heads of the fused rows `qkv` [n, (nq+2nkv)*hd] (or [S, n, ...] float32 partial sums
-    when in_splits = S > 0); rotated q goes to `q_out` [n, nq*hd], rotated k and v to the pages."""
+    when in_splits = S > 0); rotated q goes to `q_out` [n, nq*hd], rotated k and v to the pages.
+    pairing 'half': element j turns with j + rot_dim/2; 'interleaved': 2j with 2j + 1."""
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"rotary pairing {pairing!r} not supported (half, interleaved)")
     _need_cuda(qkv, q_out, positions, slots, inv_freq, k_pages, v_pages)
     width = (nq + 2 * nkv) * hd
     if in_splits:
@@ -144,7 +159,8 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, positions: torch.Tenso
     _check(lib.wllm_rope_kv_write(_ptr(qkv), _dt(qkv), row_stride, max(1, in_splits), ctypes.c_longlong(split_stride),
                                   _ptr(q_out), _dt(q_out), q_out.stride(0), _ptr(_int32(positions, "positions")),
                                   _ptr(_int32(slots, "slots") if slots is not None else None), _ptr(inv_freq),
-                                  _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size, _stream()),
+                                  _ptr(k_pages), _ptr(v_pages), n, nq, nkv, hd, rot_dim, page_size,
+                                  1 if pairing == "interleaved" else 0, _stream()),
            "rope_kv_write")
 
 
@@ -228,13 +244,13 @@ def decode_split_plan(heads: int, max_ctx: int, tile: int) -> tuple:
     def finish(keys):
         splits = -(-max_ctx // keys)
         rest, whole = max_ctx - (splits - 1) * keys, (splits - 1) * heads
-        if whole + heads <= SM_COUNT:
+        if whole + heads <= sm_count():
             return (keys if splits > 1 else rest) + per_cta
-        if whole < SM_COUNT:
-            return max(keys + per_cta, -(-heads // (SM_COUNT - whole)) * (rest + per_cta))
-        return -(-(whole + heads) // SM_COUNT) * (keys + per_cta)
-    equal = up(-(-max_ctx // max(1, SM_COUNT // heads)))
-    share = min(up(max_ctx), up(-(-max_ctx * heads // SM_COUNT)))
+        if whole < sm_count():
+            return max(keys + per_cta, -(-heads // (sm_count() - whole)) * (rest + per_cta))
+        return -(-(whole + heads) // sm_count()) * (keys + per_cta)
+    equal = up(-(-max_ctx // max(1, sm_count() // heads)))
+    share = min(up(max_ctx), up(-(-max_ctx * heads // sm_count())))
     keys = min((equal, share), key=lambda k: (finish(k), -k))
     return keys, -(-max_ctx // keys)
 
@@ -276,7 +292,7 @@ def prefill_share_plan(q_lens, ctx_lens, nq: int, nkv: int, hd: int, skip_single
         return 0
     rep = nq // nkv
     longest = max((n for n in q_lens if not (skip_single and n == 1)), default=0)
-    if longest <= 0 or -(-(longest * rep) // 128) * nkv * len(q_lens) > SM_COUNT:
+    if longest <= 0 or -(-(longest * rep) // 128) * nkv * len(q_lens) > sm_count():
         return 0
     work = heaviest = 0
     for q_len, ctx_len in zip(q_lens, ctx_lens):
@@ -287,7 +303,7 @@ def prefill_share_plan(q_lens, ctx_lens, nq: int, nkv: int, hd: int, skip_single
             walked = (pos0 + (min(rows, first + 128) - 1) // rep) // 64 + 1
             work += walked * nkv
             heaviest = max(heaviest, walked)
-    fair = max(8, -(-5 * work // (4 * SM_COUNT)))
+    fair = max(8, -(-5 * work // (4 * sm_count())))
     return fair if heaviest > fair else 0
 
 
@@ -371,7 +387,6 @@ def fma_peak_tflops(device, iters: int = 20000) -> float:
 
 _TC_EPILOGUES = {"bf16": 0, "f32": 1, "gelu_tanh": 2, "silu": 3}
 _tc_status: dict = {}
-SM_COUNT = 148
 
 
 def tc_gemm_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
@@ -399,10 +414,10 @@ def tile_plan(M: int, N: int, K: int, gated: bool = False, may_split: bool = Tru
         if half < least:
             continue
         tiles = -(-cols // (half if gated else 2 * half))
-        wanted = max(1, min(kblocks, SM_COUNT // tiles, 16)) if may_split else 1
+        wanted = max(1, min(kblocks, sm_count() // tiles, 16)) if may_split else 1
         per = -(-kblocks // wanted)
         parts = -(-kblocks // per)
-        waves = -(-(tiles * parts) // SM_COUNT)
+        waves = -(-(tiles * parts) // sm_count())
         cost = waves * (per * half + 192) * (1.0 + 0.004 * parts)
         if best is None or cost < best[0]:
             best = (cost, half, parts)
@@ -415,7 +430,7 @@ def split_plan(M: int, N: int, K: int) -> int:
 
 
 def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
-                 max_ctas: int = SM_COUNT, k_splits: int = 1, half_rows: int | None = None) -> torch.Tensor:
+                 max_ctas: int | None = None, k_splits: int = 1, half_rows: int | None = None) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
     'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
     k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums.
@@ -435,6 +450,8 @@ def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
     assert out.shape == shape and out.stride(-1) == 1 and out.dtype == (torch.float32 if code == 1 else torch.bfloat16)
     assert k_splits == 1 or (code == 1 and out.is_contiguous())
     status = _status_word(a.device)
+    if max_ctas is None:
+        max_ctas = sm_count()
     lib = load_family("gemm_bf16_tc")
     if half_rows is None:
         half_rows = tile_plan(M, N, K, code >= 2, k_splits > 1)[0]

@@ -10,7 +10,11 @@ product replaces three (the reference runs three, src/wllm/models/llama.py:103-1
 
 One forward serves whole prompts, portions and decoded tokens alike: the step's keys
 and values go into the pages first, then every token attends through its request's
-block table.
+block table.  Which kernels do that is decided here, from the step context's facts
+about the batch: 32-bit (and head sizes the tensor-core kernels are not built for)
+runs the one-warp-per-row kernel, by row or by row and chunk of keys; bfloat16 sends
+requests with one token to the split-key decode kernel and the others to the tiled
+prefill kernel, which find their requests by q_len on the device.
 """
 from __future__ import annotations
 
@@ -58,7 +62,58 @@ class PagedAttention:
         q = ctx.buffer("q_rotated", (n, self.nq * self.hd), self.model_dtype)
         ops.rope_kv_write(qkv, q, ctx.positions, ctx.group_slots[cache.group] if cache.writes else None,
                           self.position.inv_freq, k_pages, v_pages, self.nq, self.nkv, self.hd,
-                          self.position.rotary_dim, group.page_size, in_splits=parts)
+                          self.position.rotary_dim, group.page_size, in_splits=parts,
+                          pairing=getattr(self.position, "pairing", "half"))
         attn = ctx.buffer("attn", (n, self.nq * self.hd), self.model_dtype)
-        ctx.attention(q, attn, k_pages, v_pages, cache.group, self.nq, self.nkv, self.hd, self.window or 0, self.scale)
+        self.attend(q, attn, k_pages, v_pages, ctx, cache.group)
         return as_branch(ops.project(attn, self.wo, lambda name, shape, dt: ctx.buffer("branch_" + name, shape, dt)))
+
+    def attend(self, q, out, k_pages, v_pages, ctx, group: int) -> None:
+        """Attention of every token of the step over its request's pages of cache group `group`."""
+        nq, nkv, hd, window, scale = self.nq, self.nkv, self.hd, self.window or 0, self.scale
+        ps, table = ctx.cache.page_size, ctx.group_tables[group]
+        if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
+            # few rows over long contexts (decoding): a warp per (row, chunk of 64 keys) instead of a warp per row;
+            # the result is the same bit for bit, so the choice is one of speed alone
+            rows, chunks = q.shape[0] * nq, ops.simt_chunks(ctx.max_ctx, window)
+            scratch = None
+            if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
+                scratch = ctx.buffer("attention_chunks", (rows * chunks * (hd + 2),), torch.float32)
+            ops.paged_attention_simt(q, out, k_pages, v_pages, ctx.token_req, ctx.positions, table, nq, nkv, hd, ps,
+                                     window, scale, scratch, chunks)
+            return
+        decode = ctx.num_single > 0 and nq // nkv <= 16
+        if decode:
+            R = ctx.n_requests
+            # one CTA fits on an SM: every (request, kv head) is cut into parts so that the CTAs finish together
+            # (planned for the context rounded up to 512 keys, so that a growing context seldom needs a new plan)
+            split_keys, max_splits = ops.decode_split_plan(R * nkv, -(-ctx.max_ctx // 512) * 512, 32 if hd % 64 == 0 else 64)
+            scratch = ctx.buffer("attention_splits", (ops.attention_mma_scratch_floats(R, nq, hd, max_splits),),
+                                 torch.float32)
+            ops.attention_mma_decode(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
+                                     nq, nkv, hd, ps, window, scale, split_keys, max_splits, scratch)
+        if ctx.num_multi > 0 or not decode:
+            split_above, halves = self._shared_tiles(ctx, skip_single=decode)
+            ops.attention_mma_prefill(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len, table,
+                                      ctx.max_q_len, nq, nkv, hd, ps, window, scale, skip_single=decode,
+                                      split_above=split_above, halves=halves)
+
+    def _shared_tiles(self, ctx, skip_single: bool):
+        """Whether this step's prefill attention shares its heavy tiles between two CTAs (ops.prefill_share_plan),
+        and the buffer for their partial results.  Worked out once a step and head layout (kept in the step's
+        memo), not once a layer; head sizes that run on pairs of CTAs (steps of 128, more than one tile of rows)
+        never share."""
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        key = ("attention_share", nq, nkv, hd, skip_single)
+        if key not in ctx.memo:
+            if hd % 128 == 0 and ctx.max_q_len * (nq // nkv) > 128:
+                plan = 0
+            else:
+                plan = ops.prefill_share_plan(ctx.host["req_q_len"].tolist(), ctx.host["req_ctx_len"].tolist(), nq, nkv,
+                                              hd, skip_single)
+            ctx.memo[key] = plan
+        split_above = ctx.memo[key]
+        if split_above <= 0:
+            return 0, None
+        floats = ops.attention_prefill_halves_floats(ctx.n_requests, ctx.max_q_len, nq, nkv, hd)
+        return split_above, ctx.buffer("attention_halves", (floats,), torch.float32)

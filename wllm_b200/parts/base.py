@@ -18,11 +18,15 @@ Interfaces (duck-typed; see the built-in parts for examples):
                     load(fetch) where fetch(name) returns the checkpoint tensor on the device
     norm            __call__(residual: Residual, ctx) -> tensor [n, hidden] in the model dtype
                     rows(residual, rows, ctx) -> the same at selected rows only
-    position        an object the mixer of its kind understands (rotary: .inv_freq, .rotary_dim)
+    position        an object the mixer of its kind understands (rotary: .inv_freq, .rotary_dim, and
+                    optionally .pairing = 'half' | 'interleaved')
     mixer           cache_need() -> KVNeed | StateNeed | None
                     __call__(x, ctx, cache: CacheRef) -> tensor [n, hidden]
     feed-forward    __call__(x, ctx) -> tensor [n, hidden]
     block           __call__(residual, ctx, cache: CacheRef) -> None (updates the residual)
+    embedding       __call__(token_ids, ctx) -> float32 tensor [n, hidden] (the residual stream)
+    head            __init__(..., embedding) gets the model's embedding part (for a tied table);
+                    __call__(hidden_rows, ctx) -> float32 logits [rows, vocab]
 
 A part may declare `graph_safe = True`: everything it launches depends on device data and on the step's
 size bounds alone (tokens, requests, table width, longest context rounded to the table's reach), never on
@@ -133,6 +137,8 @@ class Registry(dict):
         return self[part_spec.kind](part_spec, **kwargs)
 
 
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("logits head")
 NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
 MIXERS = Registry("mixer")

@@ -14,9 +14,10 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import ParamSpec
+from .base import EMBEDDINGS, HEADS, ParamSpec
 
 
+@EMBEDDINGS.register("scaled_embedding")
 class ScaledEmbedding:
     graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype):
@@ -41,6 +42,7 @@ class ScaledEmbedding:
         return ops.embed_gather(token_ids, self.table, self.scale, out)
 
 
+@HEADS.register("logits_head")
 class LogitsHead:
     graph_safe = True
     def __init__(self, spec, hidden_size: int, model_dtype: torch.dtype, embedding: ScaledEmbedding):
