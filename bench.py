@@ -8,7 +8,9 @@ events over exactly K steps; `e2e` = the same through the Python entry point
 (`LLM.step`: pinned host index arrays in, sampled token ids out, every step);
 `prefill` = one prompt of 2,048 tokens; `roofline` = bytes a decode step has to read
 (every weight once and the live requests' cache) over its time, against the measured copy
-bandwidth; `points` = decode at batch 1 and 64.  Weights are random N(0, 0.02), token ids
+bandwidth; `points` = decode at batch 1 and 64 at the same context, at batch 1, 8 and 64 with
+1,024 cached tokens, and the headline case without captured graphs.  The headline is the median
+of `--regions` timed regions of exactly K steps each (`ms_per_step_regions` lists them all).  Weights are random N(0, 0.02), token ids
 are seeded uniform random, the caches of the device-timed runs are filled with random
 keys and values (synthetic context); the end-to-end run prefills its prompts for real.
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from
@@ -103,14 +105,17 @@ def fill_synthetic_context(runner, caches, context: int, seed: int) -> None:
             flat[i:i + n] = torch.randn(n, generator=g, device=runner.device, dtype=torch.float32).to(pages.dtype)
 
 
-def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: int, page_size: int):
-    """Device-timed decode: `steps` steps of `batch` single tokens at contexts context .. context+steps."""
+def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: int, page_size: int, regions: int = 1):
+    """Device-timed decode of `batch` single tokens a step, from `context` cached tokens on: `regions` timed
+    regions of exactly `steps` steps each, one after the other (CUDA events around each, a synchronize on both
+    sides).  Returns the median region's milliseconds per step, the kernel launches of one region, the bytes of
+    keys and values a step reads at the middle of the run, the clock samples, and every region's ms per step."""
     import torch
     from wllm_b200.engine import StepEntry, build_runner
     from wllm_b200.kernels import ops
     from wllm_b200.sampling import SamplingParams
     from wllm_b200.sampling.sampler import Sampler
-    total = context + warmup + steps + 1
+    total = context + warmup + regions * steps + 1
     pages = batch * (-(-total // page_size)) + 1
     runner = build_runner(model, engine_cfg, num_pages=pages)
     if engine_cfg.cuda_graphs:
@@ -119,7 +124,7 @@ def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: 
     caches = [runner.cache.open(i) for i in range(batch)]
     fill_synthetic_context(runner, caches, context, seed=3)
     g = torch.Generator().manual_seed(5)
-    tokens = torch.randint(0, model.plan.vocab_size, (warmup + steps, batch), generator=g).tolist()
+    tokens = torch.randint(0, model.plan.vocab_size, (warmup + regions * steps, batch), generator=g).tolist()
     greedy = [SamplingParams()] * batch
     zeros, empty = [0] * batch, [set()] * batch
 
@@ -135,26 +140,30 @@ def decode_run(model, engine_cfg, batch: int, context: int, steps: int, warmup: 
         while width * page_size < tokens:
             width *= 2
         return width
-    if engine_cfg.cuda_graphs and table_width(context + warmup + 1) != table_width(context + warmup + steps):
-        print(f"note: the timed steps cross from {table_width(context + warmup + 1)} to {table_width(context + warmup + steps)} "
-              "pages a request: one of them captures a new graph, and the time per step includes that capture", file=sys.stderr)
-    launches0, graph0 = ops.launches, runner.graph_launches
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if engine_cfg.cuda_graphs and table_width(context + warmup + 1) != table_width(context + warmup + regions * steps):
+        print(f"note: the timed steps cross from {table_width(context + warmup + 1)} to "
+              f"{table_width(context + warmup + regions * steps)} pages a request: one of them captures a new graph, and "
+              "the time per step of that region includes the capture", file=sys.stderr)
+    per_region, launches = [], 0
     with ClockSampler() as clocks:
-        torch.cuda.synchronize()
-        start.record()
-        for i in range(warmup, warmup + steps):
-            one(i)
-        end.record()
-        torch.cuda.synchronize()
-    ms = start.elapsed_time(end) / steps
-    launches = (ops.launches - launches0) + (runner.graph_launches - graph0)
-    kv_bytes = batch * (context + warmup + steps / 2.0) * runner.cache.bytes_per_token()
+        for r in range(regions):
+            launches0, graph0 = ops.launches, runner.graph_launches
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for i in range(warmup + r * steps, warmup + (r + 1) * steps):
+                one(i)
+            end.record()
+            torch.cuda.synchronize()
+            per_region.append(start.elapsed_time(end) / steps)
+            launches = (ops.launches - launches0) + (runner.graph_launches - graph0)
+    ms = statistics.median(per_region)
+    kv_bytes = batch * (context + warmup + regions * steps / 2.0) * runner.cache.bytes_per_token()
     for rc in caches:
         runner.cache.close(rc)
     del runner
     torch.cuda.empty_cache()
-    return ms, launches, kv_bytes, clocks.summary()
+    return ms, launches, kv_bytes, clocks.summary(), per_region
 
 
 def prefill_run(model, engine_cfg, tokens: int, page_size: int, repeats: int = 3):
@@ -222,11 +231,17 @@ def e2e_run(cfg, args, page_size: int):
 
 def reference_arm(args) -> int:
     """The unmodified reference from baseline/_ref through its own classes: GemmaForCausalLM with random
-    weights, KVCacheManager, Scheduler (src/wllm/engine/scheduler.py), the same batch and context.  Its
-    decode step needs its own CUDA kernel, which it builds at first use; where that build fails the arm
-    says so and exits 0."""
-    def unavailable(why: str) -> int:
-        print(json.dumps({"impl": "reference", "unavailable": " ".join(why.split())[:400]}))
+    weights, KVCacheManager, Scheduler (src/wllm/engine/scheduler.py).
+
+    Prefill: one request of 2,048 random tokens with max_new_tokens=1 goes Scheduler.step -> _prefill ->
+    prefill_with_cache... (the vendor's matrix library and torch's fused attention) and finishes there
+    (scheduler.py:276-288, 460-463): the second half of the headline metric, on the stock path.
+    Decode: needs the reference's own CUDA kernel, which it builds at first use.  Where that build fails (it
+    passes an MSVC-only flag), the decode half is `unavailable`; beside it, labelled as what it is, stands the
+    reference's model with its own plain-PyTorch attention (`_paged_attention_decode_cpu`, device-agnostic) put
+    in the kernel's place on the GPU: not the stock path, but the floor that a plain PyTorch engine reaches."""
+    def unavailable(why: str, **more) -> int:
+        print(json.dumps(dict({"impl": "reference", "unavailable": " ".join(why.split())[:400]}, **more)))
         return 0
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "wllm")):
@@ -235,22 +250,16 @@ def reference_arm(args) -> int:
     sys.path.insert(0, ref)
     try:
         import torch
+        import wllm.kernels.paged_attention as ref_attention
         from wllm.engine.kv_cache import KVCacheManager
         from wllm.engine.scheduler import Scheduler
         from wllm.engine.sequence import Sequence
-        from wllm.kernels.paged_attention import _get_ext
         from wllm.models.config import ModelConfig
         from wllm.models.gemma import GemmaForCausalLM
     except Exception as e:   # noqa: BLE001
         return unavailable(f"the reference does not import here: {type(e).__name__}: {e}")
     if not torch.cuda.is_available():
         return unavailable("no CUDA device")
-    try:
-        _get_ext()           # the reference's own JIT build of csrc/paged_attention.cu
-    except Exception as e:   # noqa: BLE001
-        first = str(e).strip().splitlines()[0] if str(e).strip() else type(e).__name__
-        return unavailable("the reference's CUDA decode kernel does not build on this box (it passes the MSVC-only "
-                           f"flag /Zc:preprocessor, src/wllm/kernels/paged_attention.py:16-20): {first}")
     c = GEMMA_2B
     cfg = ModelConfig(vocab_size=c["vocab_size"], hidden_size=c["hidden_size"], intermediate_size=c["intermediate_size"],
                       num_hidden_layers=args.layers or c["num_hidden_layers"], num_attention_heads=c["num_attention_heads"],
@@ -263,31 +272,77 @@ def reference_arm(args) -> int:
         for p in model.parameters():
             p.normal_(0, 0.02)
     model = model.to(device="cuda", dtype=torch.bfloat16).eval()
-    context = args.context or c["max_position_embeddings"] - (args.warmup + args.steps) - 2
-    blocks = args.batch * (-(-(context + args.warmup + args.steps + 2) // 16)) + 1
-    cache = KVCacheManager(cfg.num_hidden_layers, blocks, 16, cfg.num_key_value_heads, cfg.head_dim, device="cuda")
-    sched = Scheduler(model, cache, max_prefill_tokens_per_step=2048)
     g = torch.Generator().manual_seed(11)
-    for i in range(args.batch):
-        sched.add_request(Sequence(seq_id=i, prompt_token_ids=torch.randint(0, cfg.vocab_size, (context,), generator=g).tolist(),
-                                   max_new_tokens=args.warmup + args.steps + 64))
-    while sched.waiting or any(s.status.value != "running" for s in sched.running):
-        sched.step()
-    for _ in range(args.warmup):
-        sched.step()
-    torch.cuda.synchronize()
-    with ClockSampler() as clocks:
+
+    def new_cache(tokens_each: int, requests: int):
+        blocks = requests * (-(-tokens_each // 16)) + 1
+        return KVCacheManager(cfg.num_hidden_layers, blocks, 16, cfg.num_key_value_heads, cfg.head_dim, device="cuda")
+
+    # -- prefill of 2,048 tokens, stock path -----------------------------------------------------
+    T = 2048
+    sched = Scheduler(model, new_cache(T + 2, 1))
+    times = []
+    for i in range(4):
+        sched.add_request(Sequence(seq_id=i, prompt_token_ids=torch.randint(0, cfg.vocab_size, (T,), generator=g).tolist(),
+                                   max_new_tokens=1))
+        torch.cuda.synchronize()
         t0 = time.perf_counter()
-        for _ in range(args.steps):
+        done = sched.step()
+        torch.cuda.synchronize()
+        if i > 0:
+            times.append(time.perf_counter() - t0)
+        assert len(done) == 1 and done[0].is_finished()
+    prefill = {"value": round(T / min(times), 1), "tokens": T, "ms": round(min(times) * 1e3, 3),
+               "path": "Scheduler.step -> _prefill, stock"}
+    del sched
+    torch.cuda.empty_cache()
+
+    context = args.context or c["max_position_embeddings"] - (args.warmup + args.steps) - 2
+
+    def decode(steps: int, warmup: int):
+        sched = Scheduler(model, new_cache(context + warmup + steps + 66, args.batch), max_prefill_tokens_per_step=2048)
+        for i in range(args.batch):
+            sched.add_request(Sequence(seq_id=100 + i, prompt_token_ids=torch.randint(0, cfg.vocab_size, (context,), generator=g).tolist(),
+                                       max_new_tokens=warmup + steps + 64))
+        while sched.waiting or any(s.status.value != "running" for s in sched.running):
+            sched.step()
+        for _ in range(warmup):
             sched.step()
         torch.cuda.synchronize()
-        sec = (time.perf_counter() - t0) / args.steps
+        with ClockSampler() as clocks:
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                sched.step()
+            torch.cuda.synchronize()
+            sec = (time.perf_counter() - t0) / steps
+        return sec, clocks.summary()
+
+    config = {"model": "gemma-2b", "layers": cfg.num_hidden_layers, "global_batch": args.batch, "seq_len": context,
+              "page_size": 16}
+    try:
+        ref_attention._get_ext()           # the reference's own JIT build of csrc/paged_attention.cu
+    except Exception as e:   # noqa: BLE001
+        first = str(e).strip().splitlines()[0] if str(e).strip() else type(e).__name__
+        fallback = None
+        try:
+            # not the stock path: the reference's device-agnostic attention where its kernel would stand
+            ref_attention.paged_attention_decode = ref_attention._paged_attention_decode_cpu
+            sec, clocks = decode(min(args.steps, 8), 2)
+            fallback = {"value": round(args.batch / sec, 1), "unit": "tokens/s", "ms_per_step": round(sec * 1e3, 3),
+                        "steps": min(args.steps, 8), "clocks": clocks,
+                        "path": "reference model and scheduler, its plain-PyTorch attention in place of its CUDA kernel (not stock)"}
+        except Exception as e2:   # noqa: BLE001
+            fallback = {"unavailable": f"{type(e2).__name__}: {str(e2)[:200]}"}
+        return unavailable("decode: the reference's CUDA decode kernel does not build on this box (it passes the MSVC-only "
+                           f"flag /Zc:preprocessor, src/wllm/kernels/paged_attention.py:16-20): {first}",
+                           metric="Gemma-2B decode tok/s @ batch 1/8/64; prefill tok/s @ 2048 tokens", config=config,
+                           prefill=prefill, decode_torch_fallback=fallback)
+    sec, clocks = decode(args.steps, args.warmup)
     print(json.dumps({"metric": "Gemma-2B decode tok/s @ batch 1/8/64; prefill tok/s @ 2048 tokens", "impl": "reference",
                       "value": round(args.batch / sec, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 4), "higher_is_better": True,
                       "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                      "config": {"model": "gemma-2b", "layers": cfg.num_hidden_layers, "global_batch": args.batch,
-                                 "seq_len": context, "page_size": 16}, "clocks": clocks.summary()}))
+                      "config": config, "prefill": prefill, "clocks": clocks}))
     return 0
 
 
@@ -304,6 +359,7 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps steps each; the median is reported")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -320,23 +376,35 @@ def main() -> int:
     if args.layers:
         raw["num_hidden_layers"] = args.layers
     cfg = GemmaConfig.from_dict(raw)
+    args.regions = max(1, args.regions)
     if args.context is None:
-        args.context = cfg.max_position_embeddings - (args.warmup + args.steps) - 2
+        args.context = cfg.max_position_embeddings - (args.warmup + args.regions * args.steps) - 2
     ps = args.page_size
     engine_cfg = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=not args.no_graphs)
     pk = peaks()
     model = build_model(None, engine_cfg.dtype, engine_cfg.device, config=cfg, random_seed=1)
     weight_bytes = model.weight_bytes()
 
-    ms, launches, kv_bytes, clocks = decode_run(model, engine_cfg, args.batch, args.context, args.steps, args.warmup, ps)
+    ms, launches, kv_bytes, clocks, per_region = decode_run(model, engine_cfg, args.batch, args.context, args.steps,
+                                                            args.warmup, ps, args.regions)
     value = args.batch / (ms / 1e3)
     achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
 
+    # decode at batch 1 and 64 at the same context, at batch 1 / 8 / 64 with 1,024 cached tokens (the prompt length
+    # that the benchmark's configuration names), and the headline case without captured graphs; each with the
+    # fraction of the measured copy bandwidth that its bytes (weights once, the live cache) over its time come to
     points = {}
     if not args.no_points:
+        def point(name, cfg_run, b, context, regions):
+            pms, _, kvb, _, _ = decode_run(model, cfg_run, b, context, min(args.steps, 32), args.warmup, ps, regions)
+            points[name] = round(b / (pms / 1e3), 1)
+            points[name + "_hbm_frac"] = round((weight_bytes + kvb) / (pms / 1e3) / 1e9 / pk["hbm_gbs"], 3)
         for b in (1, 64):
-            pms, _, _, _ = decode_run(model, engine_cfg, b, args.context, min(args.steps, 32), args.warmup, ps)
-            points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
+            point(f"decode_b{b}", engine_cfg, b, args.context, 3)
+        for b in (1, 8, 64):
+            point(f"decode_b{b}_ctx1024", engine_cfg, b, 1024, 3)
+        eager = EngineConfig(dtype="bfloat16", block_size=ps, max_num_seqs=max(64, args.batch), cuda_graphs=False)
+        point(f"decode_b{args.batch}_no_graphs", eager, args.batch, args.context, 3)
 
     T = 2048
     pre_ms = prefill_run(model, engine_cfg, T, ps)
@@ -362,12 +430,14 @@ def main() -> int:
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "global_batch": args.batch, "seq_len": args.context, "page_size": ps, "prefill_tokens": T,
                    "cuda_graphs": not args.no_graphs, "e2e_async_scheduling": True, "parallelism": "single-gpu",
+                   "timed_regions": args.regions,
                    "l2": "inputs larger than L2 (weights %.2f GB read every step)" % (weight_bytes / 1e9),
                    "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        "ms_per_step_regions": [round(x, 4) for x in per_region],
     }
     print(json.dumps(line))
     return 0

@@ -20,9 +20,10 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LENGTHS = {"A": (7, 19, 33, 70, 41, 12, 90, 55, 66, 100), "B": (1, 4, 50, 64, 120, 37, 81, 2, 130, 77)}
 # float32: kernels and plain implementation differ in summation order only.
-# bfloat16: operands of every product are rounded to 8 bits of mantissa; logits of the
-# tiny models are of order 0.1, and the error of a row stays below 2e-2.
-TOL = {torch.float32: 3e-5, torch.bfloat16: 2e-2}
+# bfloat16: operands of every product are rounded to 8 bits of mantissa.  On these seeds the logits reach 1.6
+# (tiny A) and 2.4 (tiny B) with a standard deviation near 0.2, and the largest difference observed under any
+# cut is 1.6e-3 (A) and 1.9e-3 (B); the bound is twice the larger one.
+TOL = {torch.float32: 3e-5, torch.bfloat16: 4e-3}
 MODES = {"whole": traces.whole, "tail": traces.tail_singly, "portions": traces.portions,
          "mixed": lambda r: traces.mixed(r, seed=3)}
 
@@ -57,7 +58,8 @@ def test_every_cut_matches_plain(setups, dtype, name, mode, poison):
     pages = -(-traces.peak_tokens(steps) // ps)
     runner = gpu_runner(folder, dtype, ps, pages, poison)
     rows = traces.run_in_process(runner, steps)
-    assert max_diff(rows, ref) < TOL[dtype]
+    worst = max_diff(rows, ref)
+    assert worst < TOL[dtype], f"largest difference from the plain implementation {worst:.3e} (bound {TOL[dtype]:.0e})"
     assert runner.cache.free_pages() == [pages]
     if mode == "mixed":
         assert runner.cache.groups[0].pool.takes > pages, "the trace must use pages again"
