@@ -5,7 +5,11 @@ chunked prefill beside decoding requests, greedy decoding.
         --max-prompt 4096 --new-tokens 256 --chunk 2048
 
 Prints one JSON line: wall time, prompt and generated tokens per second, steps, preemptions, pages at the
-high-water mark.  Prompts are seeded uniform random token ids; nothing is read from disk.
+high-water mark, and the steps by kind (steps that carry prompt tokens, steps that only decode) with their
+time on the device and, for the decode steps, the bytes they have to read (every weight once and the live
+requests' keys and values) over that time.  Prompts are seeded uniform random token ids; nothing is read from
+disk.  The policy it exercises is the reference's (src/wllm/engine/scheduler.py:207-274): requests mid-prompt
+first, then new ones, under a budget of prompt tokens a step, decoding requests riding along.
 """
 from __future__ import annotations
 
@@ -59,13 +63,43 @@ def main(argv=None) -> int:
     torch.cuda.synchronize()
     for k in llm.scheduler.stats:
         llm.scheduler.stats[k] = 0
+    cache, sched = llm.runner.cache, llm.scheduler
+    page_bytes = cache.bytes_per_token() * cache.page_size
+    weight_bytes = llm.model.weight_bytes()
+    marks, loads = [], []          # an event in front of every step; (prompt tokens, decoded tokens, pages held) of the step
     start = time.perf_counter()
-    outs = llm.generate(prompts, sp)
+    reqs = [llm.add_request(p, sp) for p in prompts]
+    while llm.has_unfinished():
+        before = (sched.stats["prefill_tokens"], sched.stats["decode_tokens"])
+        mark = torch.cuda.Event(enable_timing=True)
+        mark.record()
+        llm.step()
+        held = cache.groups[0].pool.num_pages - cache.groups[0].pool.num_free
+        marks.append(mark)
+        loads.append((sched.stats["prefill_tokens"] - before[0], sched.stats["decode_tokens"] - before[1], held))
+    last = torch.cuda.Event(enable_timing=True)
+    last.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - start
+    marks.append(last)
+    outs = reqs
+    kinds = {"prompt_steps": [], "decode_steps": []}
+    decode_gbs = []
+    for i, (prompt_tokens, decoded, held) in enumerate(loads):
+        ms = marks[i].elapsed_time(marks[i + 1])
+        if prompt_tokens > 0:
+            kinds["prompt_steps"].append(ms)
+        elif decoded > 0:
+            kinds["decode_steps"].append(ms)
+            decode_gbs.append((weight_bytes + held * page_bytes) / ms / 1e6)
+    by_kind = {k: {"steps": len(v), "ms_total": round(sum(v), 1), "ms_mean": round(sum(v) / len(v), 3) if v else None}
+               for k, v in kinds.items()}
+    if decode_gbs:
+        by_kind["decode_steps"]["gbs_mean"] = round(sum(decode_gbs) / len(decode_gbs), 0)
+        by_kind["decode_steps"]["weight_gb"] = round(weight_bytes / 1e9, 2)
     from ..kernels import ops
     st = llm.stats
-    generated = sum(len(o.token_ids) for o in outs)
+    generated = sum(len(o.output_token_ids) for o in outs)
     print(json.dumps({
         "workload": "continuous batching", "shape": args.shape, "layers": cfg.num_hidden_layers, "dtype": args.dtype,
         "requests": args.requests, "prompt_tokens": sum(lengths), "generated_tokens": generated,
@@ -73,7 +107,8 @@ def main(argv=None) -> int:
         "generated_tokens_per_s": round(generated / wall, 1), "total_tokens_per_s": round((sum(lengths) + generated) / wall, 1),
         "steps": st["steps"], "preemptions": st["preemptions"], "pages_high_water": st["pages_high_water"],
         "pages": blocks, "chunk": args.chunk, "kernel_status": ops.tc_gemm_status(llm.engine_config.device),
-        "all_finished_by_length": all(o.finish_reason == "length" and len(o.token_ids) == args.new_tokens for o in outs)}))
+        "by_kind": by_kind,
+        "all_finished_by_length": all(o.finish_reason == "length" and len(o.output_token_ids) == args.new_tokens for o in outs)}))
     return 0
 
 
