@@ -673,14 +673,16 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
     }
 }
 
-// merge of the splits: grid (nq, requests).  The splits' weights exp2(m_s - M) are computed once into
-// shared memory; every thread then sums its output columns over the splits in split order.
+// merge of the splits: grid (nq, requests), one thread an output column.  A kernel of a few microseconds that
+// stands between two others, so its own chain of dependent steps is kept short: every thread first asks for its
+// column of up to 32 splits and, in the same breath, lane s of every warp for split s's maximum and sum; the
+// weights exp2(m_s - M) are then worked out by every warp for itself and handed round by shuffle, so no thread
+// waits for another warp and nothing passes through shared memory.  More than 32 splits are taken 32 at a
+// time with a running maximum.  The sums run in split order and depend on nothing but the row.
 __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* __restrict__ req_q_start,
                              const int* __restrict__ req_q_len, const int* __restrict__ req_ctx_len, int nq,
                              int split_keys, int max_splits, const float* __restrict__ part_o,
                              const float* __restrict__ part_ml) {
-    __shared__ float w[MERGE_MAX_SPLITS];
-    __shared__ float inv_l;
     pdl_begin();
     const int head = blockIdx.x, r = blockIdx.y;
     if (req_q_len[r] != 1) return;
@@ -688,33 +690,27 @@ __global__ void merge_kernel(bf16* __restrict__ out, int out_stride, const int* 
     const int num_splits = (req_ctx_len[r] + part_keys - 1) / part_keys;
     if (num_splits <= 1) return;
     const size_t slot0 = ((size_t)r * nq + head) * max_splits;
-    if (threadIdx.x < 32) {
-        float M = -INFINITY;
-        for (int s = threadIdx.x; s < num_splits; s += 32) M = fmaxf(M, part_ml[(slot0 + s) * 2]);
-        M = warp_max(M);
-        const float base = M == -INFINITY ? 0.f : M;
-        float L = 0.f;
-        for (int s = threadIdx.x; s < num_splits; s += 32) {
-            const float f = exp2f(part_ml[(slot0 + s) * 2] - base);
-            w[s] = f;
-            L += part_ml[(slot0 + s) * 2 + 1] * f;
-        }
-        L = warp_sum(L);
-        if (threadIdx.x == 0) inv_l = 1.0f / L;
-    }
-    __syncthreads();
-    // the loads of sixteen splits are issued together (they do not depend on one another); the sums run in split order
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float O = 0.f;
-        for (int s0 = 0; s0 < num_splits; s0 += 16) {
-            float p[16];
+    const int lane = threadIdx.x & 31;
+    const float2* ml = reinterpret_cast<const float2*>(part_ml) + slot0;
+    for (int d = threadIdx.x; d - lane < HD; d += blockDim.x) {   // a warp stays together (head sizes come in steps of 16)
+        const bool live = d < HD;
+        float M = -INFINITY, L = 0.f, O = 0.f;
+        for (int s0 = 0; s0 < num_splits; s0 += 32) {
+            float p[32];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) p[u] = s0 + u < num_splits ? part_o[(slot0 + s0 + u) * HD + d] : 0.f;
+            for (int u = 0; u < 32; ++u) p[u] = (live && s0 + u < num_splits) ? part_o[(slot0 + s0 + u) * HD + d] : 0.f;
+            const float2 mine = s0 + lane < num_splits ? ml[s0 + lane] : make_float2(-INFINITY, 0.f);
+            const float M_new = fmaxf(M, warp_max(mine.x));
+            const float base = M_new == -INFINITY ? 0.f : M_new;
+            const float keep = exp2f(M - base);                  // exp2(-inf) = 0 for the first group
+            const float w = exp2f(mine.x - base);
+            L = L * keep + warp_sum(mine.y * w);
+            O *= keep;
 #pragma unroll
-            for (int u = 0; u < 16; ++u)
-                if (s0 + u < num_splits) O += p[u] * w[s0 + u];
+            for (int u = 0; u < 32; ++u) O += p[u] * __shfl_sync(0xffffffffu, w, u);     // a split past the end has p = 0
+            M = M_new;
         }
-        out[(size_t)req_q_start[r] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O * inv_l);
+        if (live) out[(size_t)req_q_start[r] * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
     }
 }
 
