@@ -130,8 +130,7 @@ __device__ __forceinline__ void drain_accumulator(void* __restrict__ c, int ldc,
 template <int EPI, int AROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
-               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status,
-               int early_cap) {
+               int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status) {
     constexpr int A_BYTES = Ring<AROWS>::A_BYTES, RING_BYTES = Ring<AROWS>::RING_BYTES, MAX_STAGES = Ring<AROWS>::MAX_STAGES;
     const int B_HALF = half_rows * BK * 2, STAGE_BYTES = A_BYTES + 2 * B_HALF;
     const int STAGES = min(MAX_STAGES, RING_BYTES / STAGE_BYTES);
@@ -191,7 +190,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int mn = tile % tiles_mn, split = tile / tiles_mn;
                 const int n0 = (mn / tiles_m) * tile_n;
                 const int kb_lo = split * kb_per, kb_hi = min(kblocks, kb_lo + kb_per);
-                early = min(min(STAGES, early_cap), kb_hi - kb_lo);
+                early = min(STAGES, kb_hi - kb_lo);
                 for (int i = 0; i < early; ++i) {
                     const uint32_t b_dst = ring + i * STAGE_BYTES + A_BYTES, bar = full0 + 8 * i;
                     mbar_expect_tx(bar, STAGE_BYTES);
@@ -520,13 +519,8 @@ static int launch_rows(const CUtensorMap& ma, const CUtensorMap& mw, void* c, in
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
-    static int early_cap = -1;
-    if (early_cap < 0) {
-        const char* e = getenv("WLLM_GEMM_EARLY");
-        early_cap = e ? atoi(e) : 99;
-    }
     return wllm_launch(gemm_tc_kernel<EPI, AROWS>, ctas, NUM_THREADS, Ring<AROWS>::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
-                       up_off, k_splits, half_rows, status, early_cap);
+                       up_off, k_splits, half_rows, status);
 }
 
 // How many pairs can be resident at once.  The kernel is persistent with a fixed stride over the tiles, so
