@@ -72,7 +72,7 @@ def gemm(args) -> None:
         if parts > 1:
             ops.gemm_bf16_tc(a, w, out, "f32", k_splits=parts)
         else:
-            ops.gemm_bf16_tc(a, w, out, "f32" if args.split else code)
+            ops.gemm_bf16_tc(a, w, out, "f32" if args.split else code, half_rows=args.half_rows or None)
     ms = timed(run, args.iters)
     hbm, tf, src = peaks()
     flops, byts = 2.0 * M * N * K, (N * K + M * K) * 2.0 + out.numel() * out.element_size()
@@ -205,6 +205,7 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--epilogue", default="bf16", choices=["bf16", "f32", "gelu_tanh", "silu"])
     g.add_argument("--split", action="store_true", help="cut K into parts as a step of few rows does (float32 slabs)")
+    g.add_argument("--half-rows", type=int, default=0, help="half the W tile's rows (0: the plan's choice)")
     g32 = sub.add_parser("gemm-f32")
     g32.add_argument("--m", type=int, default=16)
     g32.add_argument("--n", type=int, default=49152)
