@@ -74,14 +74,15 @@ def test_32bit_matches_plain_and_is_bit_equal_across_cuts(model):
 
 
 def test_bfloat16_matches_plain_under_every_cut(model):
+    """Logits of up to 19 after two layers at either width; the largest difference observed under any cut is 0.022
+    (Gemma-2B widths) and 0.034 (7B): 0.12 % and 0.18 % of the scale, from bfloat16 operands over sums of 16k to
+    24k terms.  The bound is twice the larger, relative to the scale."""
     name, folder, reqs, ref = model
     scale = max(float(r.abs().max()) for r in ref.values())
     for cut, steps in cuts(reqs).items():
         rows = run(folder, torch.bfloat16, steps, ref.keys())
-        assert max_diff(rows, ref) < 0.03 * max(1.0, scale), (name, cut)
-        for k in ref:     # and the ranking of the top token survives, or is a near-tie
-            top = int(ref[k].argmax())
-            assert float(ref[k][top] - ref[k][int(rows[k].argmax())]) < 0.03 * max(1.0, scale), (name, cut, k)
+        worst = max_diff(rows, ref)
+        assert worst < 0.004 * max(1.0, scale), f"{name} {cut}: largest difference {worst:.3e} on logits of up to {scale:.1f}"
 
 
 def test_steps_queued_back_to_back_see_their_own_index_arrays(model):
@@ -103,4 +104,4 @@ def test_steps_queued_back_to_back_see_their_own_index_arrays(model):
     want = lone.step([StepEntry(lone.cache.open("x"), reqs["b"], [69])])[0].float().cpu()
     assert torch.equal(got, want)
     scale = max(float(r.abs().max()) for r in ref.values())
-    assert float((got.double() - ref[("b", 69)].double()).abs().max()) < 0.03 * max(1.0, scale)
+    assert float((got.double() - ref[("b", 69)].double()).abs().max()) < 0.004 * max(1.0, scale)
