@@ -94,6 +94,16 @@ def paged_attention_simt(q, out, k_pages, v_pages, token_req, positions, block_t
                            scale)
 
 
+def paged_attention_simt_tiled(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table, max_q_len, nq,
+                               nkv, hd, page_size, window, scale):
+    token_req, positions = [], []
+    for r, (n, c) in enumerate(zip(req_q_len.tolist(), req_ctx_len.tolist())):
+        token_req += [r] * n
+        positions += list(range(c - n, c))
+    return paged_attention(q, out, k_pages, v_pages, torch.tensor(token_req, dtype=torch.int32),
+                           torch.tensor(positions, dtype=torch.int32), block_table, nq, nkv, hd, page_size, window, scale)
+
+
 def gated_act(gate_up, out, act):
     inter = gate_up.shape[1] // 2
     g, u = gate_up[:, :inter].float(), gate_up[:, inter:].float()
@@ -135,5 +145,5 @@ def gated_linear(a, w_gate_up, act, out, scratch):
 def install(monkeypatch):
     """Replace the kernels by these functions (host-logic tests only)."""
     from wllm_b200.kernels import ops
-    for name in ("embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt", "gated_act", "gemm_f32", "linear", "project", "gated_linear"):
+    for name in ("embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt", "paged_attention_simt_tiled", "gated_act", "gemm_f32", "linear", "project", "gated_linear"):
         monkeypatch.setattr(ops, name, globals()[name])

@@ -1,7 +1,7 @@
 """Gemma-7B's layer widths in the true 32-bit path, prompts from one token to thousands, run four ways
 (each prompt whole; token by token with all prompts in one batch; portions of 512 tokens; mixed, up to four
 live requests with portions of some beside single tokens of others and so few pages that they are used
-again), logits at ALL positions:
+again; the token-by-token steps replayed from captured CUDA graphs), logits at ALL positions:
 
   * the four ways agree bit for bit (every row's digest, a 64-bit sum over the row's bit patterns);
   * the whole-prompt logits stay within a stated bound of the plain implementation, which runs on the same
@@ -73,12 +73,15 @@ def plain_weights(model, cfg: dict) -> dict:
     return w
 
 
-def run_cut(model, engine_config, steps: list, page: int, on_step=None):
+def run_cut(model, engine_config, steps: list, page: int, on_step=None, graphs: bool = False):
     """Replay a trace on a fresh cache of exactly the pages it needs.  Returns ({(request, position): digest},
-    seconds, pages at the high-water mark, pages in the pool, [(live requests, cached tokens, ms)] per step)."""
+    seconds, pages at the high-water mark, pages in the pool, [(live requests, cached tokens, ms)] per step).
+    `graphs`: steps in which every request brings one token are replayed from captured CUDA graphs."""
     from wllm_b200.engine import StepEntry, build_runner
     pages = -(-traces.peak_tokens(steps, round_to=page) // page)
     runner = build_runner(model, engine_config, num_pages=pages)
+    if graphs:
+        runner.enable_graphs()
     live, pos, keys, digests, events, loads = {}, {}, [], [], [], []
     torch.cuda.synchronize()
     start = time.perf_counter()
@@ -156,7 +159,8 @@ def test_four_ways_agree_bit_for_bit_and_with_plain():
     first, problems = None, []
     for name, steps in cuts.items():
         rows, seconds, high, pages, times = run_cut(model, engine_config, steps, size["page"],
-                                                    against_plain if name == "whole" else None)
+                                                    against_plain if name == "whole" else None,
+                                                    graphs=name == "token_by_token")
         record[name] = {"seconds": round(seconds, 2), "steps": len(steps), "pages": pages, "pages_high_water": high}
         if name == "whole":
             first = rows

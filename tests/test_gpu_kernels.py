@@ -245,6 +245,36 @@ def test_paged_attention_simt_split_by_chunks_is_the_walk_bit_for_bit(dtype, win
         assert torch.equal(split, walk)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 70])
+@pytest.mark.parametrize("case", [
+    (4, 2, 64, 16, [300, 257, 64, 3, 130], [300, 2, 33, 3, 1]),      # whole prompts, portions behind a prefix, one token
+    (8, 1, 256, 64, [200, 700], [200, 37]),                          # eight heads of a group share a tile's rows
+    (3, 3, 48, 32, [100, 65], [31, 65]),
+    (16, 16, 128, 16, [90], [90]),
+])
+def test_paged_attention_simt_tiled_is_the_walk_bit_for_bit(dtype, window, case):
+    """32 rows of a request against every tile of keys brought into shared memory once: the same numbers as a warp
+    per row, to the last bit, and the float64 statement within tolerance; rows that end inside a tile, inside a
+    chunk and on a chunk's edge, a window that starts inside a tile."""
+    nq, nkv, hd, ps, ctx_lens, q_lens = case
+    q, kp, vp, treq, pos, table = _paged_case(dtype, nq, nkv, hd, ps, ctx_lens, q_lens, seed=13, spike=(window == 0))
+    table = table.clamp(min=0)
+    scale = 1.0 / math.sqrt(hd)
+    starts = [sum(q_lens[:r]) for r in range(len(q_lens))]
+    meta = [torch.tensor(x, dtype=torch.int32, device=DEV) for x in (starts, q_lens, ctx_lens)]
+    qd, kd, vd, td = q.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV)
+    walk = torch.empty(q.shape[0], nq * hd, dtype=dtype, device=DEV)
+    ops().paged_attention_simt(qd, walk, kd, vd, treq.to(DEV), pos.to(DEV), td, nq, nkv, hd, ps, window, scale)
+    tiled = torch.full_like(walk, float("nan"))
+    ops().paged_attention_simt_tiled(qd, tiled, kd, vd, *meta, td, max(q_lens), nq, nkv, hd, ps, window, scale)
+    assert torch.equal(tiled, walk)
+    want = ref.paged_attention(q, torch.empty(q.shape[0], nq * hd, dtype=torch.float64), kp, vp, treq, pos, table,
+                               nq, nkv, hd, ps, window, scale, dtype=torch.float64)
+    t = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-5, atol=2e-5)
+    torch.testing.assert_close(tiled.cpu().double(), want, **t)
+
+
 def test_paged_attention_refuses_unsupported_head_size():
     from wllm_b200.kernels import KernelError
     q = torch.zeros(1, 40, device=DEV)

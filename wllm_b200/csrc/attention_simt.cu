@@ -21,6 +21,10 @@
 //   split    one warp per (token, head, chunk) leaves its partial result in scratch
 //            memory and a second kernel merges a row's chunks in order.  Steps of few
 //            rows over long contexts (decoding), where a walk would leave most SMs idle.
+//   tiled    a CTA takes 32 rows of one (request, key/value head) and brings every tile
+//            of 32 keys and values into shared memory once for all of them; each warp
+//            runs its four rows against the tile with the walk's arithmetic.  Portions
+//            of prompts, where neighbouring rows read the same keys.
 //
 // Used for the 32-bit path at every size, and for bfloat16 at the sizes that the
 // tensor-core kernels refuse.
@@ -83,7 +87,7 @@ __device__ __forceinline__ void chunk_partial(const float* __restrict__ qs, cons
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
         const float corr = expf(m - m_new);
-        l = l * corr + warp_sum(p);
+        l = fmaf(l, corr, warp_sum(p));
 #pragma unroll
         for (int e = 0; e < NE; ++e) o[e] *= corr;
         // values of four keys are requested before the first of them is used; a key outside the row's range
@@ -266,5 +270,222 @@ WLLM_API int wllm_paged_attention_simt(const void* q, int q_stride, void* out, i
     if (dtype == WLLM_F32)
         return launch<float>(q, q_stride, out, out_stride, k_pages, v_pages, token_req, positions, block_table, max_pages,
                              n_tokens, nq, nkv, hd, page_size, window, scale, scratch, max_chunks, stream);
+    return WLLM_BAD_DTYPE;
+}
+
+// --------------------------------------------------------------------------------------
+// tiled: grid (tiles of 32 rows, kv heads, requests); rows of a request are (token, head of the group)
+// --------------------------------------------------------------------------------------
+constexpr int TL_WARPS = 8, TL_RPW = 4, TL_ROWS = TL_WARPS * TL_RPW;
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;          // 0: the 16 bytes are filled with zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+template <typename T, int NE>
+__global__ void __launch_bounds__(TL_WARPS * 32)
+paged_attention_simt_tiled_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                                  const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                                  const int* __restrict__ req_q_start, const int* __restrict__ req_q_len,
+                                  const int* __restrict__ req_ctx_len, const int* __restrict__ block_table, int max_pages,
+                                  int nq, int nkv, int hd, int page_size, int window, float scale) {
+    constexpr int VN = Vec<T>::N;                  // elements of a 16-byte piece
+    extern __shared__ __align__(16) unsigned char tl_smem[];
+    pdl_begin();
+    const int g = blockIdx.y, r = blockIdx.z;
+    const int q_len = req_q_len[r], rep = nq / nkv, rows = q_len * rep;
+    const int m0 = blockIdx.x * TL_ROWS;
+    if (m0 >= rows) return;
+    const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kld = hd + VN;                       // a key's row in shared memory: the head and one piece of padding (banks)
+    float* qs = reinterpret_cast<float*>(tl_smem);                          // [32 rows][hd] float
+    T* ks = reinterpret_cast<T*>(qs + TL_ROWS * hd);                        // [2][32 keys][kld]
+    T* vs = ks + 2 * 32 * kld;                                              // [2][32 keys][hd]
+    const int* table = block_table + (size_t)r * max_pages;
+
+    // this warp's rows: position, first key, where they are stored
+    int pos_r[TL_RPW], first_r[TL_RPW];
+#pragma unroll
+    for (int i = 0; i < TL_RPW; ++i) {
+        const int m = m0 + warp * TL_RPW + i;
+        pos_r[i] = m < rows ? pos0 + m / rep : -1;                          // a row past the end takes no key
+        first_r[i] = window > 0 ? max(0, pos_r[i] - window + 1) : 0;
+    }
+    for (int idx = threadIdx.x; idx < TL_ROWS * hd; idx += blockDim.x) {
+        const int m = m0 + idx / hd, d = idx % hd;
+        qs[idx] = m < rows ? to_f32(q[(size_t)(q_start + m / rep) * q_stride + (size_t)(g * rep + m % rep) * hd + d]) : 0.f;
+    }
+    // the keys that the CTA's rows see, in tiles of 32 at absolute multiples of 32
+    const int last_m = min(rows, m0 + TL_ROWS) - 1;
+    const int key_hi = pos0 + last_m / rep + 1;                              // one past the last row's position
+    const int key_lo = window > 0 ? max(0, pos0 + m0 / rep - window + 1) : 0;
+    const int t_lo = key_lo >> 5, t_hi = (key_hi + 31) >> 5;
+
+    auto load_tile = [&](int t, int stage) {
+        const int pieces = hd / VN;                // 16-byte pieces of a key's row
+        for (int c = threadIdx.x; c < 32 * pieces; c += blockDim.x) {
+            const int kl = c / pieces, piece = c % pieces, key = t * 32 + kl;
+            const bool valid = key >= key_lo && key < key_hi;           // others are zero: their weight is zero, their values must be numbers
+            size_t row = 0;
+            if (valid) row = ((size_t)table[key / page_size] * nkv + g) * page_size + key % page_size;
+            cp_async_16(ks + ((size_t)stage * 32 + kl) * kld + piece * VN, k_pages + row * hd + piece * VN, valid);
+            cp_async_16(vs + ((size_t)stage * 32 + kl) * hd + piece * VN, v_pages + row * hd + piece * VN, valid);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    float m_t[TL_RPW], l_t[TL_RPW], o_t[TL_RPW][NE];      // the rows' results so far (finished chunks)
+    float m_c[TL_RPW], l_c[TL_RPW], o_c[TL_RPW][NE];      // the chunk in progress
+    bool open_c[TL_RPW];
+#pragma unroll
+    for (int i = 0; i < TL_RPW; ++i) {
+        m_t[i] = m_c[i] = -INFINITY; l_t[i] = l_c[i] = 0.f; open_c[i] = false;
+#pragma unroll
+        for (int e = 0; e < NE; ++e) o_t[i][e] = o_c[i][e] = 0.f;
+    }
+    if (t_lo < t_hi) load_tile(t_lo, 0);
+    for (int t = t_lo; t < t_hi; ++t) {
+        const int stage = (t - t_lo) & 1;
+        if (t + 1 < t_hi) load_tile(t + 1, stage ^ 1); else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();                          // tile t is here for everyone (and the queries, the first time)
+        const T* kt = ks + (size_t)stage * 32 * kld;
+        const T* vt = vs + (size_t)stage * 32 * hd;
+        const int tile = t * 32, key = tile + lane;
+        // a row takes part in the tiles from its first key's to its own position's, as in the walk
+        bool act[TL_RPW], any = false;
+#pragma unroll
+        for (int i = 0; i < TL_RPW; ++i) {
+            act[i] = !(tile > pos_r[i] || tile + 31 < first_r[i]);
+            any = any || act[i];
+        }
+        if (any) {
+            // scores of the warp's four rows against this lane's key: the key's row is read once for the four
+            // (a row that sits this tile out is computed along and dropped; every number it meets is finite)
+            const T* kr = kt + (size_t)lane * kld;
+            const float* qw = qs + (size_t)(warp * TL_RPW) * hd;
+            float acc[TL_RPW][4];
+#pragma unroll
+            for (int i = 0; i < TL_RPW; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll 4
+            for (int d = 0; d < hd; d += VN) {
+                float kv[VN];
+                Vec<T>::load(kr + d, kv);
+#pragma unroll
+                for (int i = 0; i < TL_RPW; ++i) {
+                    float qv[VN];
+#pragma unroll
+                    for (int u = 0; u < VN; u += 4) {
+                        const float4 t4 = *reinterpret_cast<const float4*>(qw + (size_t)i * hd + d + u);
+                        qv[u] = t4.x; qv[u + 1] = t4.y; qv[u + 2] = t4.z; qv[u + 3] = t4.w;
+                    }
+#pragma unroll
+                    for (int u = 0; u < VN; ++u) acc[i][u & 3] = fmaf(qv[u], kv[u], acc[i][u & 3]);
+                }
+            }
+            float p[TL_RPW];
+#pragma unroll
+            for (int i = 0; i < TL_RPW; ++i) {
+                p[i] = 0.f;
+                if (!act[i]) continue;
+                const bool valid = key >= first_r[i] && key <= pos_r[i];
+                const float s = valid ? ((acc[i][0] + acc[i][1]) + (acc[i][2] + acc[i][3])) * scale : -INFINITY;
+                const float m_new = fmaxf(m_c[i], warp_max(s));
+                p[i] = valid ? expf(s - m_new) : 0.f;
+                const float corr = expf(m_c[i] - m_new);
+                l_c[i] = fmaf(l_c[i], corr, warp_sum(p[i]));
+#pragma unroll
+                for (int e = 0; e < NE; ++e) o_c[i][e] *= corr;
+                m_c[i] = m_new;
+                open_c[i] = true;
+            }
+            // values: a key's row is read once for the four rows; a weight of 0 (a key outside a row's range, a row
+            // that sits the tile out) adds fma(0, v, o) = o
+#pragma unroll 2
+            for (int j = 0; j < 32; ++j) {
+                float v[NE];
+#pragma unroll
+                for (int e = 0; e < NE; ++e) {
+                    const int d = e * 32 + lane;
+                    v[e] = d < hd ? to_f32(vt[(size_t)j * hd + d]) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < TL_RPW; ++i) {
+                    const float pj = __shfl_sync(0xffffffffu, p[i], j);
+#pragma unroll
+                    for (int e = 0; e < NE; ++e) o_c[i][e] = fmaf(pj, v[e], o_c[i][e]);
+                }
+            }
+        }
+        // the end of a chunk of 64 keys (or of the row): its result joins the row's
+        const bool chunk_ends = ((t + 1) & (CHUNK / 32 - 1)) == 0 || t + 1 == t_hi;
+#pragma unroll
+        for (int i = 0; i < TL_RPW; ++i) {
+            if (open_c[i] && (chunk_ends || tile + 32 > pos_r[i])) {
+                merge_chunk<NE>(m_t[i], l_t[i], o_t[i], m_c[i], l_c[i], o_c[i]);
+                m_c[i] = -INFINITY; l_c[i] = 0.f; open_c[i] = false;
+#pragma unroll
+                for (int e = 0; e < NE; ++e) o_c[i][e] = 0.f;
+            }
+        }
+        __syncthreads();                          // everyone is done with this stage before the tile after next lands in it
+    }
+#pragma unroll
+    for (int i = 0; i < TL_RPW; ++i) {
+        const int m = m0 + warp * TL_RPW + i;
+        if (m < rows)
+            store_row<T, NE>(out + (size_t)(q_start + m / rep) * out_stride + (size_t)(g * rep + m % rep) * hd, hd, lane, l_t[i], o_t[i]);
+    }
+}
+
+template <typename T>
+static int launch_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages, const void* v_pages,
+                        const int* req_q_start, const int* req_q_len, const int* req_ctx_len, const int* block_table,
+                        int max_pages, int requests, int max_q_len, int nq, int nkv, int hd, int page_size, int window,
+                        float scale, cudaStream_t stream) {
+    const int rep = nq / nkv;
+    const dim3 grid((max_q_len * rep + TL_ROWS - 1) / TL_ROWS, nkv, requests);
+    const size_t smem = (size_t)TL_ROWS * hd * sizeof(float) + 2 * 32 * ((size_t)(hd + Vec<T>::N) + hd) * sizeof(T);
+#define GO(NE) do { \
+        static bool raised = false; \
+        if (!raised) { \
+            const cudaError_t e = cudaFuncSetAttribute(paged_attention_simt_tiled_kernel<T, NE>, \
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_max); \
+            if (e != cudaSuccess) return 1000 + (int)e; \
+            raised = true; \
+        } \
+        return wllm_launch(paged_attention_simt_tiled_kernel<T, NE>, grid, TL_WARPS * 32, smem, stream, (const T*)q, q_stride, \
+                           (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, req_q_start, req_q_len, req_ctx_len, \
+                           block_table, max_pages, nq, nkv, hd, page_size, window, scale); \
+    } while (0)
+    const int smem_max = TL_ROWS * 256 * (int)sizeof(float) + 2 * 32 * ((256 + Vec<T>::N) + 256) * (int)sizeof(T);
+    if (hd <= 64) GO(2);
+    if (hd <= 128) GO(4);
+    GO(8);
+#undef GO
+}
+
+// The tiled kernel for the requests of a step (all of them: a request with one token is a tile with few rows).
+// Head sizes up to 256; the result is the walk's bit for bit.
+WLLM_API int wllm_paged_attention_simt_tiled(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                             const void* v_pages, int dtype, const int* req_q_start, const int* req_q_len,
+                                             const int* req_ctx_len, const int* block_table, int max_pages, int requests,
+                                             int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
+                                             cudaStream_t stream) {
+    if (requests <= 0 || max_q_len <= 0) return WLLM_OK;
+    if (hd <= 0 || hd > 256 || hd % 16 != 0 || nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || max_pages <= 0 ||
+        nkv > 65535 || requests > 65535)
+        return WLLM_BAD_SIZE;
+    if (dtype == WLLM_BF16) {
+        if (q_stride % 8 != 0) return WLLM_BAD_ALIGN;
+        return launch_tiled<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
+                                  block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, stream);
+    }
+    if (dtype == WLLM_F32)
+        return launch_tiled<float>(q, q_stride, out, out_stride, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len,
+                                   block_table, max_pages, requests, max_q_len, nq, nkv, hd, page_size, window, scale, stream);
     return WLLM_BAD_DTYPE;
 }

@@ -120,13 +120,22 @@ def attention_f32(args) -> None:
     scratch = None
     if not args.walk and chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
         scratch = torch.empty(rows * chunks * (hd + 2), device=DEV)
-    ms = timed(lambda: ops.paged_attention_simt(q, out, k, v, treq, pos, table, nq, nkv, hd, ps, 0, 1.0 / math.sqrt(hd),
-                                                scratch, chunks), args.iters)
+    if q_len > 1 and not args.walk:          # portions of prompts: the tiled kernel, as the attention part chooses
+        starts = torch.arange(0, n, q_len, dtype=torch.int32, device=DEV)
+        qlens = torch.full((R,), q_len, dtype=torch.int32, device=DEV)
+        ctxs = torch.full((R,), ctx, dtype=torch.int32, device=DEV)
+        ms = timed(lambda: ops.paged_attention_simt_tiled(q, out, k, v, starts, qlens, ctxs, table, q_len, nq, nkv, hd, ps, 0,
+                                                          1.0 / math.sqrt(hd)), args.iters)
+        how = "tiled"
+    else:
+        ms = timed(lambda: ops.paged_attention_simt(q, out, k, v, treq, pos, table, nq, nkv, hd, ps, 0, 1.0 / math.sqrt(hd),
+                                                    scratch, chunks), args.iters)
+        how = "split by chunks" if scratch is not None else "walk"
     hbm, _, src = peaks()
     kv_bytes = 2.0 * R * ctx * nkv * hd * 4
     keys_seen = R * sum(ctx - q_len + i + 1 for i in range(q_len))
     print(f"attention f32 requests={R} context={ctx} tokens={q_len} heads={nq}/{nkv} head_dim={hd} "
-          f"{'split by chunks' if scratch is not None else 'walk'}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of keys "
+          f"{how}: {ms * 1e3:.1f} us, {kv_bytes / ms / 1e6:.0f} GB/s of keys "
           f"and values ({kv_bytes / ms / 1e6 / hbm:.3f} of {src} {hbm:.0f}), {4.0 * nq * hd * keys_seen / ms / 1e9:.2f} TFLOP/s")
 
 
@@ -220,7 +229,7 @@ def main(argv=None) -> int:
         a.add_argument("--head-dim", type=int, default=256)
         a.add_argument("--page-size", type=int, default=64)
         a.add_argument("--no-share", action="store_true", help="prefill: never share a heavy tile between two CTAs")
-        a.add_argument("--walk", action="store_true", help="attention-f32: one warp per row even where chunks would be split")
+        a.add_argument("--walk", action="store_true", help="attention-f32: one warp per row even where chunks would be split or rows tiled")
     sm = sub.add_parser("sampling")
     sm.add_argument("--rows", type=int, default=8)
     sm.add_argument("--vocab", type=int, default=256000)

@@ -202,6 +202,26 @@ def paged_attention_simt(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tens
     return out
 
 
+def paged_attention_simt_tiled(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                               req_q_start: torch.Tensor, req_q_len: torch.Tensor, req_ctx_len: torch.Tensor,
+                               block_table: torch.Tensor, max_q_len: int, nq: int, nkv: int, hd: int, page_size: int,
+                               window: int, scale: float) -> torch.Tensor:
+    """The same attention as `paged_attention_simt`, bit for bit, for steps that bring portions of prompts: a CTA
+    takes 32 rows of one (request, key/value head) and reads every tile of keys and values once for all of them
+    (csrc/attention_simt.cu, tiled).  Head sizes up to 256; requests are given by their start, length and context."""
+    _need_cuda(q, out, k_pages, v_pages, req_q_start, req_q_len, req_ctx_len, block_table)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
+    assert k_pages.is_contiguous() and v_pages.is_contiguous() and block_table.dim() == 2
+    lib = load_family("attention_simt")
+    _check(lib.wllm_paged_attention_simt_tiled(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+                                               _dt(q), _ptr(_int32(req_q_start, "req_q_start")),
+                                               _ptr(_int32(req_q_len, "req_q_len")), _ptr(_int32(req_ctx_len, "req_ctx_len")),
+                                               _ptr(_int32(block_table, "block_table")), block_table.shape[1],
+                                               req_q_len.shape[0], max_q_len, nq, nkv, hd, page_size, window, c_float(scale),
+                                               _stream()), f"paged_attention_simt_tiled(head_dim={hd}, heads={nq}/{nkv})")
+    return out
+
+
 def _indexed(device) -> torch.device:
     device = torch.device(device)
     if device.index is None and device.type == "cuda":
@@ -531,6 +551,7 @@ def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.
 
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "rope_kv_write", "paged_attention_simt",
+           "paged_attention_simt_tiled",
            "attention_mma_decode", "attention_mma_prefill", "mma_head_dim_ok", "gemm_bf16_tc", "tc_gemm_ok",
            "tc_gemm_status",
            "gated_act", "gemm_f32", "linear", "project", "gated_linear", "split_plan"]

@@ -73,8 +73,13 @@ class PagedAttention:
         nq, nkv, hd, window, scale = self.nq, self.nkv, self.hd, self.window or 0, self.scale
         ps, table = ctx.cache.page_size, ctx.group_tables[group]
         if q.dtype != torch.bfloat16 or not ops.mma_head_dim_ok(hd):
-            # few rows over long contexts (decoding): a warp per (row, chunk of 64 keys) instead of a warp per row;
-            # the result is the same bit for bit, so the choice is one of speed alone
+            # Three kernels with one result, bit for bit, so the choice is one of speed alone.  Portions of prompts:
+            # 32 rows of a request share every tile of keys.  Few rows over long contexts (decoding): a warp per
+            # (row, chunk of 64 keys).  Otherwise a warp per row.
+            if ctx.num_multi > 0 and hd <= 256:
+                ops.paged_attention_simt_tiled(q, out, k_pages, v_pages, ctx.req_q_start, ctx.req_q_len, ctx.req_ctx_len,
+                                               table, ctx.max_q_len, nq, nkv, hd, ps, window, scale)
+                return
             rows, chunks = q.shape[0] * nq, ops.simt_chunks(ctx.max_ctx, window)
             scratch = None
             if chunks > 1 and rows <= 4096 and rows * chunks <= 65536:
