@@ -117,6 +117,69 @@ def test_every_tile_shape_of_products_of_few_rows(M, half, epilogue):
         torch.testing.assert_close(got.cpu().double(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("M,N,K,half", [(300, 1000, 200, 120), (300, 1000, 200, 72), (257, 600, 136, 144), (700, 1300, 200, 144),
+                                        (512, 1100, 328, 192), (300, 1030, 200, 256), (2048, 2560, 2048, 144),
+                                        (2048, 2048, 1024, 120), (3000, 5000, 256, 144)])
+@pytest.mark.parametrize("epilogue", ["f32", "bf16"])
+def test_tile_widths_of_pairs(M, N, K, half, epilogue):
+    """On pairs of CTAs a half may be any multiple of 8, and halves of 144 to 256 rows make wide tiles (one
+    accumulator, two products a step, each CTA's half in two boxes); the last case runs several rounds of
+    wide tiles, where the products of a tile wait for the drain of the tile before."""
+    from wllm_b200.kernels import ops
+    a, w = operands(M, N, K, seed=half + M)
+    want = a.double() @ w.double().T
+    got = ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), epilogue=epilogue, half_rows=half)
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0 and got.shape == want.shape
+    if epilogue == "f32":
+        torch.testing.assert_close(got.cpu().double(), want, rtol=1e-4, atol=1e-3 * math.sqrt(K))
+        assert torch.equal(got, ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), epilogue="f32", half_rows=128))
+    else:
+        torch.testing.assert_close(got.cpu().double(), want, rtol=1e-2, atol=2e-2 * math.sqrt(K))
+
+
+def test_wide_tiles_are_refused_where_they_do_not_exist():
+    from wllm_b200.kernels import KernelError, ops
+    a, w = operands(300, 1024, 64, seed=1)
+    with pytest.raises(KernelError):
+        ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), half_rows=144, epilogue="gelu_tanh")     # the gate and up halves are the tile
+    with pytest.raises(KernelError):
+        ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), half_rows=152)                           # steps of 16 above 128
+    with pytest.raises(KernelError):
+        ops.gemm_bf16_tc(a[:100].to(DEV), w.to(DEV), half_rows=144)                      # one CTA a tile: two accumulators of 256
+    with pytest.raises(KernelError):
+        ops.gemm_bf16_tc(a[:100].to(DEV), w.to(DEV), half_rows=120)
+
+
+def test_a_wide_tile_as_the_first_product_of_a_process():
+    """How many pairs the device holds is asked of the plain form of the kernel; a process whose first product is
+    a wide one must get the same answer."""
+    import subprocess
+    import sys
+    code = ("import torch; from wllm_b200.kernels import ops; "
+            "a = torch.ones(300, 64, dtype=torch.bfloat16, device='cuda:0'); "
+            "w = torch.ones(1000, 64, dtype=torch.bfloat16, device='cuda:0'); "
+            "c = ops.gemm_bf16_tc(a, w, epilogue='f32', half_rows=144); torch.cuda.synchronize(); "
+            "assert float(c.min()) == 64.0 == float(c.max()), c; print('ok', ops.resident_pairs())")
+    done = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0 and done.stdout.startswith("ok"), done.stderr[-2000:]
+
+
+def test_the_plan_for_many_rows_saves_rounds():
+    from wllm_b200.kernels import ops
+    pairs = ops.resident_pairs()
+    for M, N, K in [(2048, 2560, 2048), (2048, 2048, 16384), (2048, 12288, 3072), (2048, 3072, 24576), (2100, 3072, 24576),
+                    (300, 2560, 2048), (129, 100, 64)]:
+        half, parts = ops.tile_plan(M, N, K, False, False)
+        assert parts == 1 and half % 16 == 0 and 64 <= half <= 256
+        rounds = lambda h: -(-(-(-M // 256) * -(-N // (2 * h))) // pairs)
+        assert rounds(half) * half <= rounds(128) * 128         # never more columns walked than with tiles of 256
+    if pairs == 74:
+        assert ops.tile_plan(2048, 2560, 2048, False, False) == (144, 1)      # 72 tiles instead of 80
+        assert ops.tile_plan(2048, 2048, 16384, False, False) == (128, 1)     # 64 tiles: nothing to save
+        assert ops.tile_plan(2048, 32768, 2048, True, False) == (128, 1)      # the gate keeps its halves
+
+
 def test_a_tile_too_small_for_the_row_count_is_refused():
     from wllm_b200.kernels import KernelError, ops
     a, w = operands(8, 256, 64, seed=1)

@@ -294,8 +294,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // Both CTAs allocate and free tensor memory together (cta_group::2), and neither leaves before the other
 // has finished (cluster barrier): its shared memory and barriers are written by the other until then.
 // ------------------------------------------------------------------------------------------------
-// Each CTA's half of the W tile has `half_rows` rows (128 unless the host found that a narrower tile fills the
-// 74 pairs better, e.g. 80 for a 2,560-column product of 2,048 rows); narrower halves deepen the ring.
+// Each CTA's half of the W tile has `half_rows` rows (128 unless the host found that another width fills the
+// pairs better); narrower halves deepen the ring.  A half of more than 128 rows (up to 256, in steps of 16) makes
+// a WIDE tile of 2 * half_rows > 256 output columns: one accumulator instead of two (so the next tile's products
+// wait for the drain of this one), two products a step of half_rows columns each, and each CTA's half as two
+// boxes of half_rows / 2 rows: rows n0 + rank * half_rows / 2 .. for the first product, the same from
+// n0 + half_rows for the second.  It pays where it saves a whole round: 2,048 x 2,560 is 80 tiles of 256 columns
+// on 74 pairs, and 72 tiles of 288.
 struct PairRing {
     static constexpr int A_BYTES = 128 * BK * 2;
     static constexpr int RING_BYTES = 6 * (A_BYTES + 128 * BK * 2);
@@ -303,7 +308,7 @@ struct PairRing {
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 256;
 };
 
-template <int EPI>
+template <int EPI, bool WIDE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, void* __restrict__ c,
                     int ldc, int M, int N, int K, int up_row_offset, int k_splits, int half_rows, int* __restrict__ status) {
@@ -325,7 +330,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int n_cols = GATED ? N / 2 : N;
     const int tile_n = GATED ? half_rows : 2 * half_rows;
     const int UP_COL = half_rows;
-    const uint32_t idesc = umma_idesc(2 * BM, 2 * half_rows, false, false);
+    constexpr bool wide = WIDE;                                // half_rows > 128
+    const int part_rows = wide ? half_rows / 2 : half_rows;    // rows of a CTA's half that one product reads
+    const uint32_t idesc = umma_idesc(2 * BM, 2 * part_rows, false, false);
     const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (n_cols + tile_n - 1) / tile_n;
     const int tiles_mn = tiles_m * tiles_n, num_tiles = tiles_mn * k_splits;
     const int kblocks = (K + BK - 1) / BK, kb_per = (kblocks + k_splits - 1) / k_splits;
@@ -343,7 +350,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t tmem_base = *tmem_slot_ptr;
     const uint32_t lead_full0 = cluster_map(full0, 0), lead_tempty0 = cluster_map(tempty0, 0);
     // this CTA's half of the W tile: rows n0.. (first CTA) or the second half / the up matrix (second CTA)
-    const int w_row_offset = rank == 0 ? 0 : (GATED ? up_row_offset : half_rows);
+    const int w_row_offset = rank == 0 ? 0 : (GATED ? up_row_offset : part_rows);
 
     if (warp == 0) {
         // ---------------- TMA producer (one in each CTA) ----------------
@@ -353,9 +360,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int early = 0;
             const bool once = tiles_m == 1;         // one tile of rows: every weight is read once, evicted first
             const uint64_t stream = l2_evict_first();
-            auto load_w = [&](uint32_t dst, uint32_t bar, int x, int y) {
+            auto load_box = [&](uint32_t dst, uint32_t bar, int x, int y) {
                 if (once) tma_load_2d_pair_hint(dst, &map_w, bar, x, y, stream);
                 else tma_load_2d_pair(dst, &map_w, bar, x, y);
+            };
+            auto load_w = [&](uint32_t dst, uint32_t bar, int x, int y) {
+                load_box(dst, bar, x, y);
+                if (wide) load_box(dst + part_rows * BK * 2, bar, x, y + half_rows);
             };
             if (pair < num_tiles) {                 // W tiles of the first stages before the predecessor has finished
                 const int mn = pair % tiles_mn, split = pair / tiles_mn;
@@ -399,7 +410,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t stage = 0, phase = 0, it = 0;
             bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
-                const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+                const uint32_t acc = wide ? 0 : it & 1, acc_phase = (wide ? it : it >> 1) & 1;
                 if (!mbar_wait(tempty0 + 8 * acc, acc_phase ^ 1)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + acc * BN;
@@ -410,9 +421,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tc_fence_after();
                     const uint32_t a_src = ring + stage * STAGE_BYTES, b_src = a_src + A_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_pair(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), idesc,
-                                    (kb > kb_lo || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint32_t fresh = (kb > kb_lo || k > 0) ? 1u : 0u;
+                        tc_mma_pair(d, smem_desc(a_src + k * UMMA_K * 2), smem_desc(b_src + k * UMMA_K * 2), idesc, fresh);
+                        if (wide)
+                            tc_mma_pair(d + half_rows, smem_desc(a_src + k * UMMA_K * 2),
+                                        smem_desc(b_src + part_rows * BK * 2 + k * UMMA_K * 2), idesc, fresh);
+                    }
                     tc_commit_pair(empty0 + 8 * stage, 3);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -427,7 +442,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         uint32_t it = 0;
         bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
-            const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+            const uint32_t acc = wide ? 0 : it & 1, acc_phase = (wide ? it : it >> 1) & 1;
             const int mn = tile % tiles_mn, split = tile / tiles_mn;
             const int m0 = (mn % tiles_m) * 2 * BM + (int)rank * BM, n0 = (mn / tiles_m) * tile_n;
             if (!mbar_wait(tfull0 + 8 * acc, acc_phase)) { ok = false; break; }
@@ -540,32 +555,45 @@ static int resident_pairs() {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<EPI>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        // asked of the plain form, whichever form is launched first: it needs its shared memory granted to answer
+        cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairRing::SMEM_BYTES);
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<EPI, false>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
         pairs = n;
     }
     return pairs;
 }
 
-template <int EPI>
-static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
-                       int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
+template <int EPI, bool WIDE>
+static int launch_pair_as(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
+                          int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              PairRing::SMEM_BYTES);
         if (e != cudaSuccess) return 1000 + (int)e;
         configured = true;
     }
-    const int resident = resident_pairs<EPI>();
+    const int resident = resident_pairs<EPI>();       // the same for both forms: it is the shared memory that decides
     if (resident < 1) return WLLM_BAD_SIZE;
     if (pairs > resident) pairs = resident;
-    return wllm_launch(gemm_tc_pair_kernel<EPI>, 2 * pairs, NUM_THREADS, PairRing::SMEM_BYTES, stream, ma, mw, c, ldc, M, N, K,
-                       up_off, k_splits, half_rows, status);
+    return wllm_launch(gemm_tc_pair_kernel<EPI, WIDE>, 2 * pairs, NUM_THREADS, PairRing::SMEM_BYTES, stream, ma, mw, c, ldc, M, N,
+                       K, up_off, k_splits, half_rows, status);
+}
+
+template <int EPI>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc, int M, int N, int K, int up_off,
+                       int k_splits, int half_rows, int* status, int pairs, cudaStream_t stream) {
+    constexpr bool GATED = EPI == EPI_GATED_GELU || EPI == EPI_GATED_SILU;
+    if constexpr (!GATED) {
+        if (half_rows > 128)
+            return launch_pair_as<EPI, true>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream);
+    }
+    return launch_pair_as<EPI, false>(ma, mw, c, ldc, M, N, K, up_off, k_splits, half_rows, status, pairs, stream);
 }
 
 // Number of CTA pairs of the two-CTA kernel that one device holds at once (for reports).
 WLLM_API int wllm_gemm_bf16_tc_resident_pairs() {
-    cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairRing::SMEM_BYTES);
+    cudaFuncSetAttribute(gemm_tc_pair_kernel<EPI_BF16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairRing::SMEM_BYTES);
     return resident_pairs<EPI_BF16>();
 }
 
@@ -595,7 +623,8 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* c, int ldc
 // = gelu_tanh(gate) * up / silu(gate) * up.  `status` is a device int that stays 0 unless a role gave up waiting.
 // k_splits > 1 needs epilogue 1 and a C of k_splits slabs [M, ldc]; every part must hold at least one block of K.
 // half_rows (a multiple of 16 up to 128; 0 = 128) sets the width of a tile: 2 * half_rows output columns, or
-// half_rows columns of the gated output (by 128 rows, or 256 rows on a pair of CTAs).
+// half_rows columns of the gated output (by 128 rows, or 256 rows on a pair of CTAs).  On pairs without a gate
+// it may also be a multiple of 8, or 144 to 256 in steps of 16 (wide tiles, see the pair kernel).
 WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, void* c, int ldc, int M, int N, int K,
                                int epilogue, int k_splits, int half_rows, int* status, int max_ctas, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return WLLM_OK;
@@ -610,11 +639,16 @@ WLLM_API int wllm_gemm_bf16_tc(const void* a, int lda, const void* w, int ldw, v
     if (gated && (N % 2 != 0)) return WLLM_BAD_SIZE;
     const bool pair = M > BM && max_ctas >= 2 && pair_enabled();
     if (half_rows == 0) half_rows = 128;
-    if (half_rows < 16 || half_rows > 128 || half_rows % 16 != 0) return WLLM_BAD_SIZE;
+    // One-CTA tiles and the gated epilogue drain halves in chunks of 16 columns; a pair's plain tile of two halves
+    // takes halves in steps of 8, and wide tiles (two products a step) halves of 144 to 256 in steps of 16.
+    const bool wide = half_rows > 128;
+    if (wide ? (!pair || gated || half_rows > 256 || half_rows % 16 != 0)
+             : (half_rows < 16 || half_rows % ((pair && !gated) ? 8 : 16) != 0))
+        return WLLM_BAD_SIZE;
     CUtensorMap ma, mw;
     int r = tensor_map(a, M, K, lda, a_rows_for(M), &ma);
     if (r) return r;
-    r = tensor_map(w, N, K, ldw, half_rows, &mw);
+    r = tensor_map(w, N, K, ldw, wide ? half_rows / 2 : half_rows, &mw);
     if (r) return r;
     const int n_cols = gated ? N / 2 : N, tile_n = gated ? half_rows : 2 * half_rows;
     if (pair) {

@@ -418,14 +418,12 @@ def tc_gemm_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 @functools.lru_cache(maxsize=4096)
 def tile_plan(M: int, N: int, K: int, gated: bool = False, may_split: bool = True) -> tuple:
-    """(half_rows, parts) for a product of at most 128 rows, which is bound by streaming W: the W tile of a
+    """(half_rows, parts).  More than 128 rows: see _pair_plan.  At most 128 rows, the product is bound by streaming W: the W tile of a
     stage is two halves of `half_rows` rows, and K is cut into `parts` (at most 16: whoever reads the partial
     sums loads that many at once).  Chosen so that tiles x parts fill the SMs evenly: the cost of a choice is
     the bytes of W that the busiest CTA streams, plus a fixed price per tile and a little per part."""
     if M > 128:
-        # pairs of CTAs on 256 x 256 tiles.  Narrower tiles were measured at the one shape where they fill the
-        # pairs better (2,048 x 2,560: 80 tiles on 74 pairs): within the noise of the full width, so no gain.
-        return 128, 1
+        return _pair_plan(M, N, K, gated), 1
     least = 48 if M <= 32 else (32 if M <= 64 else 16)     # a stage must hold the 128 rows the tensor core reads at A
     kblocks = -(-K // 64)
     cols = N // 2 if gated else N
@@ -442,6 +440,33 @@ def tile_plan(M: int, N: int, K: int, gated: bool = False, may_split: bool = Tru
         if best is None or cost < best[0]:
             best = (cost, half, parts)
     return best[1], best[2]
+
+
+@functools.lru_cache(maxsize=1)
+def resident_pairs() -> int:
+    """Pairs of CTAs of the two-CTA product that the device holds at once (74 on 148 SMs)."""
+    return max(1, int(load_family("gemm_bf16_tc").wllm_gemm_bf16_tc_resident_pairs()))
+
+
+def _pair_plan(M: int, N: int, K: int, gated: bool) -> int:
+    """half_rows for a product of more than 128 rows, on pairs of CTAs with tiles of 256 rows by 2 * half columns.
+    The pairs walk the tiles in rounds; what a round costs was fitted to measurements at 2,048 rows: a block of K
+    takes time in proportion to the bytes a CTA loads for it (its 128 rows of A and `half` rows of W: wider tiles
+    do more arithmetic per byte from the L2), and a tile's drain is hidden behind the next tile's products except
+    with wide tiles (half > 128: one accumulator), where it is paid every round.  Narrower halves than 128 were
+    measured too (no faster a block), so they only win where they save a round; with a gate the tile is the two
+    halves of 128."""
+    if gated:
+        return 128
+    pairs, kblocks, tiles_m = resident_pairs(), -(-K // 64), -(-M // 256)
+    best = None
+    for half in (128, 112, 96, 80, 64, 144, 160, 176, 192, 208, 224, 240, 256):
+        rounds = -(-(tiles_m * -(-N // (2 * half))) // pairs)
+        block_us, drain_us = 0.0017 * (128 + max(half, 128)), 1.0 + 3.0 * max(half, 128) / 128
+        cost = rounds * kblocks * block_us + (rounds if half > 128 else 1) * drain_us
+        if best is None or cost < best[0] * 0.97:          # another width must pay by 3 %
+            best = (cost, half)
+    return best[1]
 
 
 def split_plan(M: int, N: int, K: int) -> int:
