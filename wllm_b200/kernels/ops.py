@@ -234,7 +234,8 @@ def _status_word(device) -> torch.Tensor:
     device = _indexed(device)
     status = _tc_status.get(device)
     if status is None:
-        status = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):      # whoever asks first: the word is written in place from any mode later
+            status = torch.zeros(1, dtype=torch.int32, device=device)
         _tc_status[device] = status
     return status
 
