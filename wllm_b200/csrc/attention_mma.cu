@@ -732,11 +732,11 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                int skip_single, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
-    const int g = blockIdx.y, r = blockIdx.z;
+    const int g = blockIdx.x, r = blockIdx.y;                 // grid (key/value heads, requests, tiles): the longest tiles start first
     const int q_len = req_q_len[r];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
     const int rep = nq / nkv, rows = q_len * rep;
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int tile = (int)gridDim.z - 1 - (int)blockIdx.z;
     const int row0 = tile * BM;
     if (row0 >= rows) return;
     const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;   // position of the request's first new token
@@ -1000,12 +1000,13 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
         configured = true;
     }
     const int tiles = (max_q_len * (nq / nkv) + BM - 1) / BM;
+    if (requests > 65535 || 2LL * tiles > 65535) return WLLM_BAD_SIZE;      // the grid's y and z
 #if (HEAD_DIM % 64 == 0)
 #if (HEAD_DIM % 128 == 0)
     // more than one tile of 128 rows in the longest request: pairs of CTAs on 256-row tiles
     if (use_tc && use_pair && max_q_len * (nq / nkv) > TC_BM && (out_stride % 8 == 0) && (((uintptr_t)out & 15) == 0)) {
         const int pair_tiles = (max_q_len * (nq / nkv) + 2 * TC_BM - 1) / (2 * TC_BM);
-        return wllm_launch(prefill_pair_kernel, dim3(2 * pair_tiles, nkv, requests), TC_THREADS, PR_SMEM, stream,
+        return wllm_launch(prefill_pair_kernel, dim3(2 * nkv, requests, pair_tiles), TC_THREADS, PR_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, status);
     }
@@ -1017,13 +1018,13 @@ WLLM_API int wllm_attention_mma_prefill(const void* q, int q_stride, void* out, 
             arrivals = tile_arrivals_address();
             if (arrivals == nullptr) split_above = 0;
         }
-        return wllm_launch(prefill_tc_kernel, dim3(split_above > 0 ? 2 * tiles : tiles, nkv, requests), TC_THREADS, TC_SMEM, stream,
+        return wllm_launch(prefill_tc_kernel, dim3(nkv, requests, split_above > 0 ? 2 * tiles : tiles), TC_THREADS, TC_SMEM, stream,
                            (const bf16*)q, q_stride, (bf16*)out, out_stride, km, vm, req_q_start, req_q_len, req_ctx_len,
                            block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E, skip_single, split_above, halves,
                            arrivals, status);
     }
 #endif
-    return wllm_launch(prefill_kernel, dim3(tiles, nkv, requests), PRE_THREADS, PRE_SMEM, stream,
+    return wllm_launch(prefill_kernel, dim3(nkv, requests, tiles), PRE_THREADS, PRE_SMEM, stream,
                        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, km, vm,
                        req_q_start, req_q_len, req_ctx_len, block_table, max_pages, nq, nkv, page_size, window, scale * LOG2E,
                        skip_single, status);

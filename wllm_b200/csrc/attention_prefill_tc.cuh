@@ -54,14 +54,16 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     extern __shared__ unsigned char smem_raw[];
     __shared__ int s_second;
     pdl_begin();
-    const int g = blockIdx.y, r = blockIdx.z;
+    // grid (key/value heads, requests, tiles): CTAs start in the order x, y, z, so the tiles that walk the most
+    // keys (the last rows of every head and request) start first and the short ones fill the SMs behind them
+    const int g = blockIdx.x, r = blockIdx.y;
     const int q_len = req_q_len[r];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;
     const int rep = nq / nkv, rows = q_len * rep;
     // With split_above > 0 the grid holds two CTAs a tile; a tile that walks more than split_above key tiles
     // is shared between them (each takes half of its keys), the second CTA of any other tile leaves at once.
     const int parts = split_above > 0 ? 2 : 1;
-    const int slot_x = (int)gridDim.x - 1 - (int)blockIdx.x;
+    const int slot_x = (int)gridDim.z - 1 - (int)blockIdx.z;
     const int tile = slot_x / parts, part = slot_x % parts;
     const int row0 = tile * TC_BM;
     if (row0 >= rows) return;
@@ -296,7 +298,7 @@ prefill_tc_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
             // (every softmax thread passes the two block barriers below, whatever its own waits came to)
             // Every lane of a warp takes part in the loads, rows past the end too; only their stores are left out.
             tc_fence_after();
-            const int item = (r * nkv + g) * ((int)gridDim.x / 2) + tile;
+            const int item = (r * nkv + g) * ((int)gridDim.z / 2) + tile;
             // a half result: [column chunk of 32][row][32] (a warp writes whole lines), then (maximum, sum) by row
             float* mine = halves + (size_t)(item * 2 + part) * TC_BM * (HD + 4);
             const float* other = halves + (size_t)(item * 2 + (part ^ 1)) * TC_BM * (HD + 4);
@@ -415,12 +417,14 @@ prefill_pair_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__
                     int skip_single, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     pdl_begin();
-    const int g = blockIdx.y, r = blockIdx.z;
+    // grid (2 x key/value heads, requests, tiles): the pairs start in the order x, y, z, the tiles that walk the most
+    // keys (the last rows of every head and request) first, so that the short ones fill the SMs behind them
+    const int g = blockIdx.x >> 1, r = blockIdx.y;
     const int q_len = req_q_len[r];
     if (q_len <= 0 || (skip_single && q_len == 1)) return;             // the same for both CTAs of a pair
     const int rep = nq / nkv, rows = q_len * rep;
     const uint32_t rank = cluster_ctarank();
-    const int tile = (int)(gridDim.x >> 1) - 1 - (int)(blockIdx.x >> 1);
+    const int tile = (int)gridDim.z - 1 - (int)blockIdx.z;
     if (tile * 2 * TC_BM >= rows) return;
     const int row0 = tile * 2 * TC_BM + (int)rank * TC_BM;             // may lie past the end: then all rows are masked
     const int ctx = req_ctx_len[r], q_start = req_q_start[r], pos0 = ctx - q_len;
