@@ -120,6 +120,50 @@ def test_budget_cuts_prompts_and_decodes_ride_along():
         assert r.output_token_ids == expected_output(r.prompt_token_ids, r.sampling.max_tokens)
 
 
+def test_the_budget_is_cut_back_to_whole_tiles_of_rows_when_that_gives_more_prompt_tokens_a_tile():
+    """row_quantum 8, budget 16.  Alone, a prompt takes 16 tokens a step (two tiles of rows).  With 3 requests
+    decoding beside it, 16 + 3 rows would be three tiles for 16 prompt tokens; 13 + 3 are two tiles for 13: more a
+    tile, so the step takes 13.  With 7 decoding, 9 + 7 = two tiles would give 4.5 a tile against 16 / 3: the budget
+    stays.  Outputs are the same as without the quantum."""
+    s, runner = make(pages=64, budget=16, row_quantum=8, max_model_len=64)
+    decoders = [req(i, 2, 12) for i in range(3)]
+    for r in decoders:
+        s.add_request(r)
+    s.step()                                   # three short prompts, whole: 6 prompt tokens
+    assert runner.batches[0] == [(0, 2, [1]), (1, 2, [1]), (2, 2, [1])]
+    long = req(9, 40, 2)
+    s.add_request(long)
+    s.step()
+    assert runner.batches[1] == [(0, 1, [0]), (1, 1, [0]), (2, 1, [0]), (9, 13, [])]        # 3 + 13 = 16 rows
+    s.step()
+    assert runner.batches[2][-1] == (9, 13, [])
+    more = [req(20 + i, 2, 12) for i in range(4)]
+    for r in more:
+        s.add_request(r)
+    s.step()                                   # the long prompt's 13, and of the four new ones what the cut budget leaves
+    assert sum(n for _, n, _ in runner.batches[3]) % 8 == 0
+    s.run_to_completion()
+    for r in decoders + more + [long]:
+        assert r.output_token_ids == expected_output(r.prompt_token_ids, r.sampling.max_tokens)
+    # seven riders: the cut would leave 9 prompt tokens on two tiles, fewer a tile than 16 on three
+    s2, runner2 = make(pages=64, budget=16, row_quantum=8, max_model_len=64)
+    riders = [req(i, 2, 12) for i in range(7)]
+    for r in riders:
+        s2.add_request(r)
+    s2.step()
+    s2.add_request(req(9, 40, 2))
+    s2.step()
+    assert runner2.batches[1][-1] == (9, 16, [])
+    # off: the budget as it is
+    s3, runner3 = make(pages=64, budget=16, max_model_len=64)
+    for r in [req(i, 2, 12) for i in range(3)]:
+        s3.add_request(r)
+    s3.step()
+    s3.add_request(req(9, 40, 2))
+    s3.step()
+    assert runner3.batches[1][-1] == (9, 16, [])
+
+
 def test_portions_down_to_one_token():
     s, runner = make(budget=1)
     a = req(0, 3, 2)

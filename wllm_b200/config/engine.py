@@ -31,6 +31,8 @@ class EngineConfig:
     block_size: int = 16                 # tokens per cache page
     num_blocks: int = 256                # pages in each cache group's pool
     chunked_prefill_tokens: int | None = None   # token budget of one step; None = whole prompts
+    prefill_row_quantum: int | None = None     # rows of a tile of the products of a step of many rows (scheduler: 'rows');
+                                               # None: 256 under bfloat16 (pairs of CTAs), off under float32
     max_num_seqs: int = 256              # requests that may be live at once (table rows, state slots)
     max_model_len: int | None = None     # None: the model's max_position_embeddings
     cuda_graphs: bool = False            # replay captured graphs for decode-only steps
@@ -45,5 +47,9 @@ class EngineConfig:
             raise ConfigError("num_blocks must be at least 1")
         if self.chunked_prefill_tokens is not None and self.chunked_prefill_tokens < 1:
             raise ConfigError("chunked_prefill_tokens must be at least 1 (or None for whole prompts)")
+        if self.prefill_row_quantum is None:
+            self.prefill_row_quantum = 256 if self.dtype == torch.bfloat16 else 0
+        if self.prefill_row_quantum < 0:
+            raise ConfigError("prefill_row_quantum must be 0 (off) or a number of rows")
         if self.max_num_seqs < 1:
             raise ConfigError("max_num_seqs must be at least 1")

@@ -17,6 +17,12 @@ Policy, with the reference's rule beside it:
               already prefilling come first, in order of admission, then new ones, each
               taking min(budget left, tokens left) (scheduler.py:215-257).  Decoded
               tokens ride along uncounted.  None: whole prompts.
+  rows        `row_quantum` (no counterpart in the reference; 0 = off): the matrix products of a
+              step of many rows work on tiles of that many rows (256 for the bfloat16 products
+              on pairs of CTAs), so 2,048 prompt tokens beside 52 decoded ones cost nine tiles
+              of rows where 1,996 cost eight.  When the budget and the decoded tokens together
+              pass a multiple of the quantum, the budget of that step is cut back to the
+              multiple if that gives more prompt tokens a tile; the tokens cut come next step.
   pages out   the step reserves all its pages first; on OutOfPages the youngest live
               request is preempted: its pages go back, it returns to the FRONT of the
               queue and is later run again from its prompt plus the tokens it has
@@ -48,11 +54,12 @@ from .runner import StepEntry
 class Scheduler:
     def __init__(self, runner, sampler, chunked_prefill_tokens: int | None = None, max_num_seqs: int = 256,
                  max_model_len: int | None = None, admission: str = "worst_case", seed: int = 0,
-                 async_scheduling: bool = False):
+                 async_scheduling: bool = False, row_quantum: int = 0):
         if admission not in ("worst_case", "optimistic"):
             raise ValueError("admission must be 'worst_case' or 'optimistic'")
         self.runner, self.sampler, self.cache = runner, sampler, runner.cache
         self.budget = chunked_prefill_tokens
+        self.row_quantum = int(row_quantum)
         self.max_num_seqs = min(max_num_seqs, self.cache.slots.num_slots)
         self.max_model_len = max_model_len or runner.model.plan.max_positions
         self.admission = admission
@@ -141,15 +148,34 @@ class Scheduler:
         return victim
 
     # -- one step ----------------------------------------------------------------------------
+    def _last_in_flight(self, r: Request) -> bool:
+        """With pipelining: the token in flight is the request's last, so it brings nothing to this step."""
+        return bool(r.inflight) and (len(r.output_token_ids) + 1 >= r.sampling.max_tokens
+                                     or r.num_tokens + 1 >= self.max_model_len)
+
+    def _step_budget(self) -> int:
+        """The prompt tokens this step may take: the budget, cut back to where the step's rows (decoded tokens ride
+        along) are a multiple of `row_quantum` when that gives more prompt tokens per tile of rows."""
+        if self.budget is None:
+            return 1 << 60
+        q, budget = self.row_quantum, self.budget
+        if q <= 0:
+            return budget
+        riding = sum(1 for r in self.live if r.status == RequestStatus.RUNNING and not self._last_in_flight(r))
+        rows = budget + riding
+        cut = rows // q * q - riding
+        if rows % q == 0 or rows < q or cut < 1:
+            return budget
+        return cut if cut * -(-rows // q) > budget * (rows // q) else budget      # cut / tiles' > budget / tiles
+
     def _plan(self):
         """(request, first token index, count) for this step; admits from the queue."""
-        budget = self.budget if self.budget is not None else 1 << 60
+        budget = self._step_budget()
         plan, taken = [], 0
         for r in self.live:
             left = r.num_tokens + r.inflight - r.num_computed
             if r.status == RequestStatus.RUNNING:
-                if r.inflight and (len(r.output_token_ids) + 1 >= r.sampling.max_tokens
-                                   or r.num_tokens + 1 >= self.max_model_len):
+                if self._last_in_flight(r):
                     continue                               # the token in flight is its last
                 plan.append((r, r.num_computed, left))     # its newest token (one), outside the budget
                 continue

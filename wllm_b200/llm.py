@@ -36,13 +36,13 @@ class LLM:
                  dtype="bfloat16", block_size: int = 16, num_blocks: int = 256,
                  chunked_prefill_tokens: int | None = None, max_num_seqs: int = 256, max_model_len: int | None = None,
                  cuda_graphs: bool = False, device: str = "cuda:0", admission: str = "worst_case", seed: int = 0,
-                 async_scheduling: bool = False, poison_pages: bool = False):
+                 async_scheduling: bool = False, poison_pages: bool = False, prefill_row_quantum: int | None = None):
         """`model`: a folder with config.json and model.safetensors.  Without it, `config` (a typed
         configuration) and `random_seed` make a model with random weights on the device."""
         self.engine_config = EngineConfig(dtype=dtype, block_size=block_size, num_blocks=num_blocks,
                                           chunked_prefill_tokens=chunked_prefill_tokens, max_num_seqs=max_num_seqs,
                                           max_model_len=max_model_len, cuda_graphs=cuda_graphs, device=device,
-                                          poison_pages=poison_pages)
+                                          poison_pages=poison_pages, prefill_row_quantum=prefill_row_quantum)
         ec = self.engine_config
         self.model = build_model(model, ec.dtype, ec.device, config=config, random_seed=random_seed)
         self.runner = build_runner(self.model, ec, poison_pages=ec.poison_pages)
@@ -51,7 +51,7 @@ class LLM:
         self.sampler = Sampler(ec.device)
         self.scheduler = Scheduler(self.runner, self.sampler, chunked_prefill_tokens=chunked_prefill_tokens,
                                    max_num_seqs=max_num_seqs, max_model_len=max_model_len, admission=admission, seed=seed,
-                                   async_scheduling=async_scheduling)
+                                   async_scheduling=async_scheduling, row_quantum=ec.prefill_row_quantum)
         self.eos_token_id = self.model.plan.eos_token_id
         self._next_id = 0
 
