@@ -73,16 +73,19 @@ def test_refuses_what_it_cannot_take():
         ops.gemm_bf16_tc(a, torch.zeros(16, 20, dtype=torch.bfloat16, device=DEV))
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 2048, 2048), (8, 2560, 2048), (64, 2048, 16384), (1, 512, 200), (33, 300, 1024)])
+@pytest.mark.parametrize("M,N,K", [(8, 2048, 2048), (8, 2560, 2048), (64, 2048, 16384), (1, 512, 200), (33, 300, 1024),
+                                   (100, 2560, 2048), (128, 2048, 16384), (256, 2048, 16384), (300, 2560, 2048), (512, 2048, 2048),
+                                   (700, 3072, 24576)])
 def test_split_k_partial_sums(M, N, K):
+    """Up to 128 rows on single CTAs, above on pairs: the parts of K that the plan gives, slab by slab."""
     from wllm_b200.kernels import ops
     a, w = operands(M, N, K, seed=K + M)
     want = a.double() @ w.double().T
-    parts = ops.split_plan(M, N, K)
+    half, parts = ops.product_plan(M, N, K)
     assert parts >= 1 and (K <= 64 or parts > 1)
     out = torch.full((parts, M, N), float("nan"), device=DEV)
     if parts > 1:
-        ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), out=out, epilogue="f32", k_splits=parts)
+        ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), out=out, epilogue="f32", k_splits=parts, half_rows=half)
     else:
         ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), out=out[0], epilogue="f32")
     torch.cuda.synchronize()
@@ -90,7 +93,7 @@ def test_split_k_partial_sums(M, N, K):
     total = out.cpu().double().sum(0)
     torch.testing.assert_close(total, want, rtol=1e-4, atol=1e-3 * math.sqrt(K))
     again = torch.empty_like(out)
-    ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), out=again if parts > 1 else again[0], epilogue="f32", k_splits=parts)
+    ops.gemm_bf16_tc(a.to(DEV), w.to(DEV), out=again if parts > 1 else again[0], epilogue="f32", k_splits=parts, half_rows=half)
     assert torch.equal(again, out)        # part s is the same sum whoever computes it
 
 

@@ -66,6 +66,7 @@ class ModelRunner:
             raise RuntimeError("the model's weights are not loaded")
         self.model, self.cache, self.device = model, cache, torch.device(device)
         self._arena: dict = {}
+        self._views: dict = {}         # (name, shape, dtype) -> the view handed out before
         self._ring = PinnedRing(self.device)
         self._meta = None
         self.steps = 0
@@ -77,6 +78,11 @@ class ModelRunner:
         self.graph_launches = 0        # kernel launches replayed from graphs so far
 
     def workspace(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        """A scratch tensor of that shape at the front of the arena's buffer of that name and type (the same memory
+        for every shape asked under the name; the buffer grows when a larger one is asked for)."""
+        view = self._views.get((name, shape, dtype))
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= s
@@ -85,7 +91,12 @@ class ModelRunner:
         if buf is None or buf.numel() < n:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._arena[key] = buf
-        return buf[:n].view(shape)
+            for k in [k for k in self._views if k[0] == name and k[2] == dtype]:
+                del self._views[k]                  # views of the buffer that this one replaces
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[(name, shape, dtype)] = buf[:n].view(shape)
+        return view
 
     # -- batch building --------------------------------------------------------------
     def _host_arrays(self, entries: list, table_width: int | None, pad_requests: int | None):
@@ -282,8 +293,8 @@ class ModelRunner:
             rec = self._graphs.get(key)         # the send may have had to grow the buffer, which drops the captures
         if rec is None:
             ctx = self._build(entries, table_width=width, device_tokens=device_tokens, pad_requests=bucket)
-            arena, saved = {}, self._arena
-            self._arena = arena
+            arena, saved, saved_views = {}, self._arena, self._views
+            self._arena, self._views = arena, {}     # the capture's buffers are its own: eager steps do not write them
             try:
                 self.model.forward(ctx)                  # loads kernels and library handles outside the capture
                 torch.cuda.synchronize()
@@ -295,7 +306,7 @@ class ModelRunner:
                        "meta": self._meta}
                 ops.launches = before
             finally:
-                self._arena = saved
+                self._arena, self._views = saved, saved_views
             self._graphs[key] = rec
         rec["graph"].replay()
         self.graph_launches += rec["launches"]

@@ -35,6 +35,7 @@ class KernelBuildError(RuntimeError):
 
 
 _loaded: dict[str, ctypes.CDLL] = {}
+_plain: dict[str, ctypes.CDLL] = {}          # families built without defines, by name alone
 _lock = threading.Lock()
 
 
@@ -147,6 +148,10 @@ def compile_family(family: str, defines: dict | None = None, verbose: bool = Tru
 
 def load_family(family: str, defines: dict | None = None) -> ctypes.CDLL:
     """The loaded library of a kernel family (compiled on first use)."""
+    if not defines:
+        lib = _plain.get(family)          # the common case, asked at every launch: no key to build, no lock
+        if lib is not None:
+            return lib
     key = family + repr(sorted((defines or {}).items()))
     with _lock:
         lib = _loaded.get(key)
@@ -157,6 +162,8 @@ def load_family(family: str, defines: dict | None = None) -> ctypes.CDLL:
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from e
             _loaded[key] = lib
+        if not defines:
+            _plain[family] = lib
         return lib
 
 

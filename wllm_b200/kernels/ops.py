@@ -470,19 +470,35 @@ def _pair_plan(M: int, N: int, K: int, gated: bool) -> int:
     return best[1]
 
 
+def product_plan(M: int, N: int, K: int) -> tuple:
+    """(half_rows, parts) for a projection whose reader adds partial sums: up to 128 rows tile_plan's choice; above,
+    pairs of CTAs, and K is cut into parts as long as the tiles leave at least half of the pairs idle (a prompt of
+    256 tokens has 8 tiles of its down projection for 74 pairs): as many parts as fit, of at least 8 blocks of K."""
+    if M <= 128:
+        return tile_plan(M, N, K)
+    half = _pair_plan(M, N, K, False)
+    pairs, kblocks = resident_pairs(), -(-K // 64)
+    tiles = -(-M // 256) * -(-N // (2 * half))
+    wanted = min(pairs // tiles, kblocks // 8, 16)
+    if wanted < 2:
+        return half, 1
+    per = -(-kblocks // wanted)
+    return half, -(-kblocks // per)
+
+
 def split_plan(M: int, N: int, K: int) -> int:
     """Parts to cut K into so that a product of few rows still gives every SM a share of the weights."""
-    return tile_plan(M, N, K)[1]
+    return product_plan(M, N, K)[1]
 
 
 def gemm_bf16_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, epilogue: str = "bf16",
-                 max_ctas: int | None = None, k_splits: int = 1, half_rows: int | None = None) -> torch.Tensor:
+                 max_ctas: int | None = None, k_splits: int = 1, half_rows: int | None = None, checked: bool = False) -> torch.Tensor:
     """out = a @ w^T on tcgen05 tensor cores (csrc/gemm_bf16_tc.cu).  epilogue 'bf16' | 'f32' (32-bit out) |
     'gelu_tanh' | 'silu' (w = [gate; up] stacked: out[M, N/2] = act(a gate^T) * (a up^T)).
     k_splits > 1 ('f32' only) cuts K into parts; `out` is then [k_splits, M, N] partial sums.
     half_rows: the tile of products of at most 128 rows (see tile_plan, which chooses it when None)."""
     _need_cuda(a, w, out)
-    if not tc_gemm_ok(a, w):
+    if not checked and not tc_gemm_ok(a, w):        # `checked`: the caller has asked tc_gemm_ok already
         raise KernelError("gemm_bf16_tc: bfloat16 operands with K and row pitches in steps of 8 elements, 16-byte "
                           f"aligned; got a{tuple(a.shape)} stride {a.stride()} w{tuple(w.shape)} stride {w.stride()}")
     M, K = a.shape
@@ -525,7 +541,7 @@ def reset_kernel_status(device) -> None:
         status.zero_()
 
 
-TC_MIN_ROWS = 65   # below this a step is bound by streaming the weights; see linear()
+TC_MIN_ROWS = 65   # fewer rows outside project(): the vendor's library (see linear())
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, f32_out: bool = False) -> torch.Tensor:
@@ -541,7 +557,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, f3
         return gemm_f32(a, w, out)
     _need_cuda(a, w)
     if tc_gemm_ok(a, w) and (a.shape[0] >= TC_MIN_ROWS or f32_out):
-        return gemm_bf16_tc(a, w, out, "f32" if f32_out else "bf16")
+        return gemm_bf16_tc(a, w, out, "f32" if f32_out else "bf16", checked=True)
     global launches
     launches += 1
     r = torch.matmul(a, w.t(), out=out) if out is not None and not f32_out else torch.matmul(a, w.t())
@@ -551,18 +567,16 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None, f3
 def project(a: torch.Tensor, w: torch.Tensor, buffer) -> tuple:
     """a @ w^T for a layer's projections whose reader can add partial sums itself (the norm and the rotary
     kernels do).  Returns (tensor, parts).  parts = 0: `tensor` is the plain product [n, N] in the operands'
-    type.  parts = S > 0 (bfloat16 steps of few rows, which are bound by streaming the weights): `tensor`
-    is [S, n, N] float32 partial sums over S parts of K, left by a split-K run of the tensor-memory GEMM in
-    which every SM takes a share.  `buffer(name, shape, dtype)` supplies the output."""
+    type.  parts = S > 0 (bfloat16 steps whose tiles alone would leave most SMs idle: up to 128 rows, which are
+    bound by streaming the weights, and short prompts): `tensor` is [S, n, N] float32 partial sums over S parts of
+    K, left by a split-K run of the tensor-memory GEMM in which every SM takes a share.  `buffer(name, shape, dtype)` supplies the output."""
     n, N = a.shape[0], w.shape[0]
-    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w) and n < TC_MIN_ROWS:
-        parts = split_plan(n, N, a.shape[1])
-        out = buffer("parts", (parts, n, N), torch.float32)
-        if parts == 1:
-            gemm_bf16_tc(a, w, out[0], "f32")
-        else:
-            gemm_bf16_tc(a, w, out, "f32", k_splits=parts)
-        return out, parts
+    if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w):
+        half, parts = product_plan(n, N, a.shape[1])
+        if n <= 128 or parts > 1:
+            out = buffer("parts", (parts, n, N), torch.float32)
+            gemm_bf16_tc(a, w, out if parts > 1 else out[0], "f32", k_splits=parts, half_rows=half, checked=True)
+            return out, parts
     return linear(a, w, buffer("product", (n, N), a.dtype)), 0
 
 
@@ -571,7 +585,7 @@ def gated_linear(a: torch.Tensor, w_gate_up: torch.Tensor, act: str, out: torch.
     tensor-memory GEMM whose epilogue applies the activation; otherwise product, then activation kernel
     (`scratch(shape, dtype)` supplies the [n, 2I] intermediate)."""
     if a.dtype == torch.bfloat16 and tc_gemm_ok(a, w_gate_up):
-        return gemm_bf16_tc(a, w_gate_up, out, act)
+        return gemm_bf16_tc(a, w_gate_up, out, act, checked=True)
     gu = linear(a, w_gate_up, scratch((a.shape[0], w_gate_up.shape[0]), a.dtype))
     return gated_act(gu, out, act)
 
