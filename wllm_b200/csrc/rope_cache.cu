@@ -13,7 +13,7 @@
 // Page layout: [page][kv_head][slot_in_page][head_dim]; `slots[n]` is page * page_size + slot_in_page.
 #include "common.cuh"
 
-// Two launch shapes.  Few tokens (a decode step): grid (token, head), so that the heads of a token run on
+// Two launch shapes.  Fewer than 1,024 tokens (a decode step, a short prompt): grid (token, head), so that the heads of a token run on
 // different SMs; head < nq rotates a query head into q_out, nq <= head < nq + nkv rotates a key head into
 // its page, the rest copy a value head into its page.  Many tokens: one CTA a token (ALL_HEADS), which
 // computes the sines and cosines of the token's position once and walks the heads with them.
@@ -146,7 +146,10 @@ WLLM_API int wllm_rope_kv_write(const void* qkv, int in_dtype, int row_stride, i
                            (bf16*)q_out, q_stride, positions, slots, inv_freq, (bf16*)k_pages, (bf16*)v_pages, nq, nkv, hd,
                            rot_dim, page_size);
     const int threads = hd >= 256 ? 128 : (hd >= 128 ? 64 : 32);
-    const bool all_heads = n >= 256;         // enough tokens to fill the SMs with one CTA each
+    // One CTA a token once the tokens alone fill the SMs several times over; below that a CTA a head, which keeps a
+    // token's heads (and the partial sums each has to add) on different SMs: 256 tokens x 10 heads of 4 parts took
+    // 24 us a layer as 256 CTAs and take 6 as 2,560.
+    const bool all_heads = n >= 1024;
     const dim3 grid(n, all_heads ? 1 : nq + 2 * nkv);
 #define GO2(TI, TO, A) wllm_launch(rope_kv_write_kernel<TI, TO, A>, grid, threads, 0, stream, (const TI*)qkv, row_stride, in_splits, \
         (size_t)in_split_stride, (TO*)q_out, q_stride, positions, slots, inv_freq, (TO*)k_pages, (TO*)v_pages, nq, nkv, hd, \
