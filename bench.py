@@ -197,31 +197,37 @@ def prefill_flops(cfg, layers: int, tokens: int) -> float:
 
 
 def e2e_run(cfg, args, page_size: int):
-    """The same decode through LLM.add_request / LLM.step: real prefill of the prompts, then timed steps."""
+    """The same decode through LLM.add_request / LLM.step: real prefill of the prompts, then `--regions` timed
+    regions of exactly K steps each by the host's clock (a synchronize on both sides of each); the median region
+    is reported, as for the device-timed number."""
     import torch
     from wllm_b200 import LLM, SamplingParams
     # requests that finish their prompt early decode while the others still prefill: leave room for that
     prefill_steps = args.batch * (-(-args.context // 2048)) + 1
-    context = min(args.context, cfg.max_position_embeddings - (args.warmup + args.steps) - prefill_steps - 4)
-    total = context + args.warmup + args.steps + prefill_steps + 4
+    timed = args.regions * args.steps
+    context = min(args.context, cfg.max_position_embeddings - (args.warmup + timed) - prefill_steps - 4)
+    total = context + args.warmup + timed + prefill_steps + 4
     llm = LLM(None, config=cfg, random_seed=1, dtype="bfloat16", block_size=page_size,
               num_blocks=args.batch * (-(-total // page_size)) + 1, chunked_prefill_tokens=2048,
               max_num_seqs=max(args.batch, 8), cuda_graphs=not args.no_graphs, async_scheduling=True)
     g = torch.Generator().manual_seed(11)
-    sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + args.steps + prefill_steps + 2, ignore_eos=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=args.warmup + timed + prefill_steps + 2, ignore_eos=True)
     for _ in range(args.batch):
         llm.add_request(torch.randint(0, cfg.vocab_size, (context,), generator=g).tolist(), sp)
     while any(r.status.value != "running" for r in llm.scheduler.live) or llm.scheduler.waiting:
         llm.step()
     for _ in range(args.warmup):
         llm.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        got = llm.step()       # launches this step, then reads the tokens of the step before (pipelined)
-        assert len(got) == args.batch
-    torch.cuda.synchronize()
-    sec = (time.perf_counter() - t0) / args.steps
+    per_region = []
+    for _ in range(args.regions):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            got = llm.step()       # launches this step, then reads the tokens of the step before (pipelined)
+            assert len(got) == args.batch
+        torch.cuda.synchronize()
+        per_region.append((time.perf_counter() - t0) / args.steps)
+    sec = sorted(per_region)[len(per_region) // 2]
     h2d = llm.runner.h2d_bytes + llm.sampler.h2d_bytes
     d2h = llm.sampler.d2h_bytes
     del llm
