@@ -470,6 +470,7 @@ def _pair_plan(M: int, N: int, K: int, gated: bool) -> int:
     return best[1]
 
 
+@functools.lru_cache(maxsize=4096)
 def product_plan(M: int, N: int, K: int) -> tuple:
     """(half_rows, parts) for a projection whose reader adds partial sums: up to 128 rows tile_plan's choice; above,
     pairs of CTAs, and K is cut into parts as long as the tiles leave at least half of the pairs idle (a prompt of
