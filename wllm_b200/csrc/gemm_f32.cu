@@ -154,7 +154,13 @@ gemm_f32_tile_kernel(const float* __restrict__ A, int lda, const float* __restri
 // skinny kernel (K and the pitches in steps of 4 floats, 16-byte aligned operands)
 // ------------------------------------------------------------------------------------------------
 constexpr int SBN = 32, SBK = 32, SLD = SBK + 4;    // a warp's stage: 32 rows of 32 floats (128 contiguous bytes of W) + 4 of padding
-constexpr int SWARPS = 4, SSTAGES = 4;
+constexpr int SWARPS = 4;
+// Stages of a warp's ring.  Four (12 KB of W a warp ahead of its arithmetic, two CTAs an SM) is what a launch with
+// tasks for every warp slot runs fastest with.  A launch of few tasks (the o projection of a 32-bit Gemma-7B step
+// is 384 tasks for 148 SMs) lives on what each warp has in flight: it takes the deep ring, as deep as four warps'
+// shared memory allows (28 KB a warp with up to 8 rows of A, 20 KB with 16; with 32 rows there is no room).
+constexpr int SSTAGES_FULL = 4;
+template <int BM> __host__ __device__ constexpr int skinny_deep_stages() { return BM <= 8 ? 8 : (BM <= 16 ? 6 : 4); }
 
 __device__ __forceinline__ void cp_async_16(float* smem_dst, const float* src, bool valid) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -166,7 +172,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 // A warp's task: rows n0..n0+31 of W, segment `seg`.  Lane x keeps BM chains, out[m][n0 + x], m < BM.
 // `dst` is C when K has one segment, else the partial sums [segment][M][N].
-template <int BM>
+template <int BM, int SSTAGES>
 __global__ void __launch_bounds__(SWARPS * 32)
 gemm_f32_skinny_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
                        float* __restrict__ dst, int ld_dst, long long seg_stride, int M, int N, int K, int segs,
@@ -256,26 +262,43 @@ gemm_f32_fold_kernel(const float* __restrict__ parts, float* __restrict__ C, int
     C[(idx / N) * ldc + idx % N] = total;
 }
 
-template <int BM>
-static int launch_skinny(const float* A, int lda, const float* W, int ldw, float* C, int ldc, int M, int N, int K,
-                         float* scratch, long long scratch_floats, cudaStream_t stream) {
+template <int BM, int STAGES>
+static int launch_skinny_as(const float* A, int lda, const float* W, int ldw, float* C, int ldc, int M, int N, int K,
+                            float* scratch, cudaStream_t stream) {
     const int segs = (K + SEG - 1) / SEG;
-    if (segs > 1 && (scratch == nullptr || scratch_floats < (long long)segs * M * N)) return WLLM_BAD_SIZE;
-    const size_t smem = (size_t)SWARPS * SSTAGES * (SBN + BM) * SLD * sizeof(float);
+    const size_t smem = (size_t)SWARPS * STAGES * (SBN + BM) * SLD * sizeof(float);
     static bool raised = false;          // per instantiation; the attribute is a property of the function
     if (!raised) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_f32_skinny_kernel<BM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_f32_skinny_kernel<BM, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                    (int)smem);
         if (e != cudaSuccess) return 1000 + (int)e;
         raised = true;
     }
     const int tasks = ((N + SBN - 1) / SBN) * segs;
     float* dst = segs > 1 ? scratch : C;
-    const int st = wllm_launch(gemm_f32_skinny_kernel<BM>, dim3((tasks + SWARPS - 1) / SWARPS), SWARPS * 32, smem, stream, A,
-                               lda, W, ldw, dst, segs > 1 ? N : ldc, (long long)M * N, M, N, K, segs, tasks);
+    const int st = wllm_launch(gemm_f32_skinny_kernel<BM, STAGES>, dim3((tasks + SWARPS - 1) / SWARPS), SWARPS * 32, smem, stream,
+                               A, lda, W, ldw, dst, segs > 1 ? N : ldc, (long long)M * N, M, N, K, segs, tasks);
     if (st != WLLM_OK || segs == 1) return st;
     return wllm_launch(gemm_f32_fold_kernel, dim3((unsigned)(((size_t)M * N + 255) / 256)), 256, 0, stream,
                        (const float*)scratch, C, ldc, M, N, segs);
+}
+
+template <int BM>
+static int launch_skinny(const float* A, int lda, const float* W, int ldw, float* C, int ldc, int M, int N, int K,
+                         float* scratch, long long scratch_floats, cudaStream_t stream) {
+    const int segs = (K + SEG - 1) / SEG;
+    if (segs > 1 && (scratch == nullptr || scratch_floats < (long long)segs * M * N)) return WLLM_BAD_SIZE;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            sms = 148;
+    }
+    const int tasks = ((N + SBN - 1) / SBN) * segs;
+    constexpr int DEEP = skinny_deep_stages<BM>();
+    if (DEEP != SSTAGES_FULL && tasks <= sms * SWARPS)      // at most one CTA's worth of warps an SM: few tasks
+        return launch_skinny_as<BM, DEEP>(A, lda, W, ldw, C, ldc, M, N, K, scratch, stream);
+    return launch_skinny_as<BM, SSTAGES_FULL>(A, lda, W, ldw, C, ldc, M, N, K, scratch, stream);
 }
 
 template <int BM, bool VEC>
