@@ -462,9 +462,9 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
 // --------------------------------------------------------------------------------------
 // decode, warp-specialised (head sizes in steps of 64): grid (max_splits, nkv, requests)
 // --------------------------------------------------------------------------------------
-// One producer warp and three consumer warps.  The producer's elected lane walks the split's keys in
+// One producer warp and six consumer warps.  The producer's elected lane walks the split's keys in
 // tiles of 32 and fills a ring of six stages with TMA box copies (keys and values of one tile per stage);
-// tile n goes to consumer warp n % 3, which waits for it on the stage's "full" mbarrier, runs all 16
+// tile n goes to consumer warp n % 6, which waits for it on the stage's "full" mbarrier, runs all 16
 // query rows against its 32 keys, and hands the stage back through the "empty" mbarrier.  No barrier
 // spans the CTA until the running states are merged at the end, so a warp that waits for memory or for
 // a dependent instruction stalls nobody else, and several tiles are in flight behind those in use.
@@ -582,7 +582,7 @@ decode_ws_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ ou
             if (!ok) atomicExch(status, GAVE_UP_DECODE);
         }
     } else {
-        // ---------------- consumers: warp w takes tiles w, w + 3, ... ----------------
+        // ---------------- consumers: warp w takes tiles w, w + 6, ... ----------------
         const int first_r[2] = {key_lo, key_lo};
         const int hi_r[2] = {min(pos, key_hi - 1), min(pos, key_hi - 1)};
         for (int n = warp; t0 + n < t1; n += WS_CONSUMERS) {
