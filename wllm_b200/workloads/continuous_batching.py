@@ -42,6 +42,9 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--async-scheduling", action="store_true", help="launch each step before the previous step's tokens are read")
+    ap.add_argument("--page-fraction", type=float, default=1.0,
+                    help="of the pages that all requests would need at their ends (below 1: requests wait, or are preempted)")
+    ap.add_argument("--admission", default="worst_case", choices=["worst_case", "optimistic"])
     args = ap.parse_args(argv)
 
     from .. import LLM, SamplingParams
@@ -55,9 +58,10 @@ def main(argv=None) -> int:
     lengths = torch.randint(args.min_prompt, args.max_prompt + 1, (args.requests,), generator=g).tolist()
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lengths]
     blocks = sum(-(-(n + args.new_tokens) // args.block_size) for n in lengths) + 1
+    blocks = max(int(blocks * args.page_fraction), -(-(max(lengths) + args.new_tokens) // args.block_size) + 1)
     llm = LLM(None, config=cfg, random_seed=1, dtype=args.dtype, block_size=args.block_size, num_blocks=blocks,
               chunked_prefill_tokens=args.chunk, max_num_seqs=args.requests, cuda_graphs=not args.no_graphs,
-              async_scheduling=args.async_scheduling)
+              async_scheduling=args.async_scheduling, admission=args.admission)
     sp = SamplingParams(temperature=0.0, max_tokens=args.new_tokens, ignore_eos=True)
     llm.generate(prompts[:2], SamplingParams(max_tokens=4, ignore_eos=True))        # warm-up: kernels, graphs
     torch.cuda.synchronize()
