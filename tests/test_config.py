@@ -67,6 +67,10 @@ def test_round_trip_through_to_dict():
 def test_engine_config_checks():
     assert EngineConfig(dtype="float32").dtype.is_floating_point
     for bad in (dict(block_size=24), dict(block_size=8), dict(num_blocks=0), dict(dtype="float16"),
-                dict(chunked_prefill_tokens=0)):
+                dict(chunked_prefill_tokens=0), dict(prefill_row_quantum=-1)):
         with pytest.raises(ConfigError):
             EngineConfig(**bad)
+    # the scheduler's tile of rows follows the element type unless it is given
+    assert EngineConfig(dtype="bfloat16").prefill_row_quantum == 256
+    assert EngineConfig(dtype="float32").prefill_row_quantum == 0
+    assert EngineConfig(dtype="bfloat16", prefill_row_quantum=0).prefill_row_quantum == 0
