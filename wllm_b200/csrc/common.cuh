@@ -26,6 +26,14 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// One rotary pair turned by the angle whose sine and cosine are given: every product and sum rounded on its own
+// (no contraction that one kernel's compilation might make and another's not), so that every kernel that rotates
+// gives the same bits.
+__device__ __forceinline__ void rotate_pair(float x1, float x2, float sn, float cs, float& y1, float& y2) {
+    y1 = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));
+    y2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+}
+
 static inline int wllm_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? WLLM_OK : 1000 + (int)e;

@@ -68,8 +68,10 @@ __global__ void rope_kv_write_kernel(const TI* __restrict__ qkv, int row_stride,
             if (j != (int)threadIdx.x) sincosf(pos * inv_freq[j], &sn, &cs);
             const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + half;
             const float x1 = in(ia), x2 = in(ib);
-            dst[ia] = from_f32<TO>(x1 * cs - x2 * sn);
-            dst[ib] = from_f32<TO>(x2 * cs + x1 * sn);
+            float y1, y2;
+            rotate_pair(x1, x2, sn, cs, y1, y2);
+            dst[ia] = from_f32<TO>(y1);
+            dst[ib] = from_f32<TO>(y2);
         }
         for (int c = rot_dim + threadIdx.x; c < hd; c += blockDim.x) dst[c] = from_f32<TO>(in(c));
     }
@@ -114,8 +116,10 @@ __global__ void rope_kv_write_rows_kernel(const bf16* __restrict__ qkv, int row_
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const float x1 = to_f32(xa[e]), x2 = to_f32(xb[e]), sn = sc[j + e], cs = sc[half + j + e];
-            pa[e] = from_f32<bf16>(x1 * cs - x2 * sn);
-            pb[e] = from_f32<bf16>(x2 * cs + x1 * sn);
+            float y1, y2;
+            rotate_pair(x1, x2, sn, cs, y1, y2);
+            pa[e] = from_f32<bf16>(y1);
+            pb[e] = from_f32<bf16>(y2);
         }
         bf16* dst = dst_of(h);
         *reinterpret_cast<uint4*>(dst + j) = ya;
