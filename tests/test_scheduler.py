@@ -326,6 +326,19 @@ def test_pipelined_with_budget_preemption_and_late_arrivals():
         assert a.output_token_ids == b.output_token_ids == expected_output(a.prompt_token_ids, a.sampling.max_tokens)
 
 
+def test_pipelined_with_a_row_quantum_budget_and_preemption():
+    """The cut of the budget to whole tiles of rows counts the requests that ride along; with tokens in flight those
+    whose last token is in flight ride no more.  Outputs are what they are without pipelining and without the cut."""
+    def requests():
+        return [req(0, 7, 9), req(1, 6, 9), req(2, 23, 3), req(3, 5, 2)]
+    (s0, run0, plain), (s1, run1, piped) = run_both(requests, pages=12, budget=9, admission="optimistic", row_quantum=4)
+    for a, b in zip(plain, piped):
+        assert a.output_token_ids == b.output_token_ids == expected_output(a.prompt_token_ids, a.sampling.max_tokens)
+    # a step that took the cut has a multiple of four rows
+    cut = [b for b in run0.batches if sum(n for _, n, _ in b) % 4 == 0 and any(n > 1 for _, n, _ in b) and any(n == 1 for _, n, _ in b)]
+    assert cut, run0.batches
+
+
 def test_pipelined_repetition_penalty_sees_every_earlier_token():
     s, _ = make(async_scheduling=True)
     a = Request(0, [3, 4, 5], SamplingParams(max_tokens=4, repetition_penalty=1.3))
