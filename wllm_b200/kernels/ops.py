@@ -474,13 +474,13 @@ def _pair_plan(M: int, N: int, K: int, gated: bool) -> int:
 def product_plan(M: int, N: int, K: int) -> tuple:
     """(half_rows, parts) for a projection whose reader adds partial sums: up to 128 rows tile_plan's choice; above,
     pairs of CTAs, and K is cut into parts as long as the tiles leave at least half of the pairs idle (a prompt of
-    256 tokens has 8 tiles of its down projection for 74 pairs): as many parts as fit, of at least 8 blocks of K."""
+    256 tokens has 8 tiles of its down projection for 74 pairs): as many parts as fit, of at least 4 blocks of K."""
     if M <= 128:
         return tile_plan(M, N, K)
     half = _pair_plan(M, N, K, False)
     pairs, kblocks = resident_pairs(), -(-K // 64)
     tiles = -(-M // 256) * -(-N // (2 * half))
-    wanted = min(pairs // tiles, kblocks // 8, 16)
+    wanted = min(pairs // tiles, kblocks // 4, 16)
     if wanted < 2:
         return half, 1
     per = -(-kblocks // wanted)
