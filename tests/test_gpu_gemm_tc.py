@@ -141,6 +141,24 @@ def test_tile_widths_of_pairs(M, N, K, half, epilogue):
         torch.testing.assert_close(got.cpu().double(), want, rtol=1e-2, atol=2e-2 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 3072, 4096), (2048, 12288, 3072), (2100, 3072, 24576), (2048, 2560, 2048), (4096, 2560, 2048)])
+def test_the_planned_widths_at_the_shapes_of_gemma_7b_and_2b(M, N, K):
+    """The widths that the plan picks for prompts at the real shapes (halves of 144 to 240 rows), against a float64
+    product of the same operands formed on the device, and bit-equal to tiles of 256 columns."""
+    from wllm_b200.kernels import ops
+    g = torch.Generator(device=DEV).manual_seed(M + N)
+    a = (torch.randn(M, K, generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g, device=DEV) * 0.5).to(torch.bfloat16)
+    half, _ = ops.tile_plan(M, N, K, False, False)
+    got = ops.gemm_bf16_tc(a, w, epilogue="f32")
+    torch.cuda.synchronize()
+    assert ops.tc_gemm_status(DEV) == 0
+    assert torch.equal(got, ops.gemm_bf16_tc(a, w, epilogue="f32", half_rows=128)), half
+    rows = torch.tensor([0, 1, 127, 128, 255, 256, M // 2, M - 1], device=DEV)
+    want = a[rows].double() @ w.double().T
+    torch.testing.assert_close(got[rows].double(), want, rtol=1e-4, atol=1e-3 * math.sqrt(K))
+
+
 def test_wide_tiles_are_refused_where_they_do_not_exist():
     from wllm_b200.kernels import KernelError, ops
     a, w = operands(300, 1024, 64, seed=1)
